@@ -1,0 +1,260 @@
+// extern "C" entry points of include/aotriton_b200.h: host-side validation,
+// translation of the POD argument structs into kernel parameters, and the choice
+// between the tcgen05 kernels and the general kernels.  No device memory is
+// allocated here, nothing synchronises, and there is no CPU path: if no kernel can
+// take the problem the call fails with an error code.
+//
+// Error vocabulary follows ROCm/aotriton (python/codegen/template/op.cc:21-71):
+// unknown GPU -> hipErrorNoBinaryForGpu (209), unsupported functional ->
+// hipErrorNotSupported (801), malformed arguments -> hipErrorInvalidValue (1).
+#include <atomic>
+#include <mutex>
+#include <cstdio>
+#include <cstdlib>
+
+#include "../../include/aotriton_b200.h"
+#include "launch.h"
+
+namespace ab200 {
+
+static std::atomic<uint64_t> g_launches{0};
+static thread_local int g_family = 0;   // per calling thread, so concurrent callers do not interfere
+static thread_local int t_last_fwd = 0, t_last_bwd = 0;
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+namespace {
+
+enum : int { kErrInvalidValue = 1, kErrNoBinaryForGpu = 209, kErrNotSupported = 801 };
+
+struct DeviceInfo { int major = 0, minor = 0, sms = 0; bool known = false; };
+
+// Device properties are immutable, so a racy double initialisation is harmless; the
+// mutex only keeps the table itself consistent.
+DeviceInfo device_info(int dev) {
+  static std::mutex mu;
+  static DeviceInfo table[64];
+  if (dev < 0 || dev >= 64) return DeviceInfo{};
+  std::lock_guard<std::mutex> lock(mu);
+  if (!table[dev].known) {
+    DeviceInfo d;
+    if (cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&d.minor, cudaDevAttrComputeCapabilityMinor, dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) {
+      d.known = true;
+      table[dev] = d;
+    } else {
+      (void)cudaGetLastError();
+    }
+  }
+  return table[dev];
+}
+
+int stream_device(cudaStream_t st) {
+  int dev = -1;
+#if CUDART_VERSION >= 12080
+  if (st != nullptr && cudaStreamGetDevice(st, &dev) == cudaSuccess) return dev;
+  (void)cudaGetLastError();
+#endif
+  if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+  return dev;
+}
+
+int check_device(cudaStream_t st) {
+  int dev = stream_device(st);
+  if (dev < 0) return kErrNoBinaryForGpu;
+  DeviceInfo d = device_info(dev);
+  if (!d.known || d.major != 10) return kErrNoBinaryForGpu;   // kernels are built for sm_100a only
+  return 0;
+}
+
+View4 to_view(const ab200_view4& v) {
+  View4 r; r.ptr = v.ptr;
+  for (int i = 0; i < 4; ++i) r.s[i] = v.stride[i];
+  return r;
+}
+
+bool inner_contiguous(const ab200_view4& v) { return v.ptr == nullptr || v.stride[3] == 1; }
+
+int fill_common(const ab200_attn_problem& a, Params& p) {
+  if (a.dtype < AB200_DTYPE_FP32 || a.dtype > AB200_DTYPE_BF16) return kErrNotSupported;
+  if (a.batch < 0 || a.num_head_q <= 0 || a.num_head_k <= 0 || a.max_seqlen_q < 0 || a.max_seqlen_k < 0)
+    return kErrInvalidValue;
+  if (a.head_dim_qk <= 0 || a.head_dim_vo <= 0) return kErrInvalidValue;
+  if (a.head_dim_qk > 512 || a.head_dim_vo > 512) return kErrNotSupported;   // head-dim rounding fails beyond 512
+  if (a.num_head_q % a.num_head_k != 0) return kErrInvalidValue;
+  if (a.causal_type < 0 || a.causal_type > 3) return kErrNotSupported;
+  if (!(a.dropout_p >= 0.f) || a.dropout_p > 1.f) return kErrInvalidValue;
+  p.batch = a.batch; p.hq = a.num_head_q; p.hk = a.num_head_k; p.group = a.num_head_q / a.num_head_k;
+  p.max_sq = a.max_seqlen_q; p.max_sk = a.max_seqlen_k; p.dqk = a.head_dim_qk; p.dvo = a.head_dim_vo;
+  p.sm_scale = a.sm_scale; p.qk_scale = a.sm_scale * kLog2e;
+  p.dropout_p = a.dropout_p;
+  p.dropout_on = a.dropout_p > 0.f ? 1 : 0;
+  p.dropout_scale = p.dropout_on ? 1.0f / (1.0f - a.dropout_p) : 1.0f;
+  p.idropout = p.dropout_on ? dropout_threshold(a.dropout_p) : 0;
+  p.causal_type = a.causal_type; p.causal = a.causal_type != 0;
+  p.window_left = a.window_left; p.window_right = a.window_right;
+  p.cu_q = a.cu_seqlens_q; p.cu_k = a.cu_seqlens_k; p.ss_q = a.seq_strides_q; p.ss_k = a.seq_strides_k;
+  if (a.cu_seqlens_q != nullptr) {
+    if (a.cu_seqlens_k == nullptr) return kErrInvalidValue;
+    if ((a.seq_strides_q == nullptr) != (a.seq_strides_k == nullptr)) return kErrInvalidValue;
+    p.varlen_mode = a.varlen_type == AB200_VARLEN_PADDED ? 2 : 1;
+    if (p.varlen_mode == 2) { p.ss_q = nullptr; p.ss_k = nullptr; }
+  } else {
+    p.varlen_mode = 0; p.ss_q = nullptr; p.ss_k = nullptr; p.cu_k = nullptr;
+  }
+  p.seed_ptr = a.philox_seed; p.off1_ptr = a.philox_offset1; p.off2 = a.philox_offset2;
+  p.philox_head_offset = a.philox_head_offset; p.philox_hq = a.philox_num_head_q;
+  return 0;
+}
+
+bool want_sm100(int family) { return family != 1; }
+
+}  // namespace
+}  // namespace ab200
+
+using namespace ab200;
+
+extern "C" {
+
+int ab200_check_gpu(void* stream) { return check_device(static_cast<cudaStream_t>(stream)); }
+
+int ab200_multiprocessor_count(void* stream) {
+  int dev = stream_device(static_cast<cudaStream_t>(stream));
+  if (dev < 0) return 0;
+  return device_info(dev).sms;
+}
+
+int ab200_set_kernel_family(int family) {
+  int old = g_family;
+  if (family >= 0 && family <= 2) g_family = family;
+  return old;
+}
+int ab200_last_fwd_family(void) { return t_last_fwd; }
+int ab200_last_bwd_family(void) { return t_last_bwd; }
+uint64_t ab200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+const char* ab200_version(void) { return "aotriton_b200 0.1 (sm_100a; API level of aotriton 0.14)"; }
+
+int ab200_debug_simulate_encoded_softmax(const ab200_view4* r, int32_t dtype, int32_t batch, int32_t num_head_q,
+                                         int32_t rows, int32_t cols, float dropout_p, const uint64_t* philox_seed,
+                                         const uint64_t* philox_offset1, uint64_t philox_offset2, void* stream) {
+  if (r == nullptr || r->ptr == nullptr) return kErrInvalidValue;
+  if (dtype < AB200_DTYPE_FP32 || dtype > AB200_DTYPE_BF16) return kErrNotSupported;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int e = check_device(st)) return e;
+  return (int)launch_dropout_sign(dtype, to_view(*r), batch, num_head_q, rows, cols, dropout_p, philox_seed,
+                                  philox_offset1, philox_offset2, st);
+}
+
+int ab200_attn_fwd(const ab200_attn_fwd_args* a, void* stream) {
+  if (a == nullptr) return kErrInvalidValue;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Params p{};
+  if (int e = fill_common(a->prob, p)) return e;
+  if (!a->q.ptr || !a->k.ptr || !a->v.ptr || !a->out.ptr) return kErrInvalidValue;
+  if (!inner_contiguous(a->q) || !inner_contiguous(a->k) || !inner_contiguous(a->v) || !inner_contiguous(a->out))
+    return kErrInvalidValue;
+  if (int e = check_device(st)) return e;
+  p.q = to_view(a->q); p.k = to_view(a->k); p.v = to_view(a->v); p.out = to_view(a->out);
+  p.bias = to_view(a->bias); p.has_bias = a->bias.ptr != nullptr;
+  p.lse = a->lse;
+  p.seed_out = a->philox_seed_output; p.off_out = a->philox_offset_output;
+
+  const int family = g_family;
+  cudaError_t err;
+  if (want_sm100(family) && sm100_fwd_supported(a->prob.dtype, p)) {
+    err = launch_sm100_fwd(a->prob.dtype, p, st);
+    t_last_fwd = 2;
+  } else {
+    if (family == 2) return kErrNotSupported;
+    err = launch_general(0, a->prob.dtype, p, st);
+    t_last_fwd = 1;
+  }
+  if (err != cudaSuccess) return (int)err;
+  if (a->encoded_softmax.ptr != nullptr) {
+    // The mask dump reuses the forward's head count, Max_seqlen_q/k and Philox inputs
+    // (modules/flash/csrc/attn_debug.cc:13-29): rows/cols passed here size the grid only.
+    View4 r = to_view(a->encoded_softmax);
+    err = launch_dropout_sign(a->prob.dtype, r, p.batch, p.hq, p.max_sq, p.max_sk, p.dropout_p, p.seed_ptr,
+                              p.off1_ptr, p.off2, st);
+  }
+  return (int)err;
+}
+
+static int fill_bwd(const ab200_attn_bwd_args* a, Params& p, bool need_outputs) {
+  if (a == nullptr) return kErrInvalidValue;
+  if (int e = fill_common(a->prob, p)) return e;
+  if (!a->out.ptr || !a->dout.ptr || !a->delta) return kErrInvalidValue;
+  if (!inner_contiguous(a->out) || !inner_contiguous(a->dout)) return kErrInvalidValue;
+  p.out = to_view(a->out); p.dout = to_view(a->dout); p.delta = a->delta;
+  p.lse = const_cast<float*>(a->lse);
+  if (need_outputs) {
+    if (!a->q.ptr || !a->k.ptr || !a->v.ptr || !a->lse) return kErrInvalidValue;
+    if (!inner_contiguous(a->q) || !inner_contiguous(a->k) || !inner_contiguous(a->v) || !inner_contiguous(a->dq) ||
+        !inner_contiguous(a->dk) || !inner_contiguous(a->dv))
+      return kErrInvalidValue;
+  }
+  p.q = to_view(a->q); p.k = to_view(a->k); p.v = to_view(a->v);
+  p.bias = to_view(a->bias); p.has_bias = a->bias.ptr != nullptr;
+  p.dq = to_view(a->dq); p.dk = to_view(a->dk); p.dv = to_view(a->dv); p.dbias = to_view(a->dbias);
+  // dBias is skipped when absent or when all its strides are zero
+  // (modules/flash/kernel/bwd_kernel_dq.py:265-266).
+  p.has_dbias = a->dbias.ptr != nullptr &&
+                (a->dbias.stride[0] | a->dbias.stride[1] | a->dbias.stride[2] | a->dbias.stride[3]) != 0;
+  return 0;
+}
+
+int ab200_bwd_preprocess(const ab200_attn_bwd_args* a, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Params p{};
+  if (int e = fill_bwd(a, p, false)) return e;
+  if (int e = check_device(st)) return e;
+  return (int)launch_preprocess(a->prob.dtype, p, st);
+}
+
+int ab200_bwd_dkdv(const ab200_attn_bwd_args* a, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Params p{};
+  if (int e = fill_bwd(a, p, true)) return e;
+  if (!a->dk.ptr || !a->dv.ptr) return kErrInvalidValue;
+  if (int e = check_device(st)) return e;
+  const int family = g_family;
+  if (want_sm100(family) && sm100_bwd_supported(a->prob.dtype, p)) {
+    t_last_bwd = 2;
+    return (int)launch_sm100_bwd_dkdv(a->prob.dtype, p, st);
+  }
+  if (family == 2) return kErrNotSupported;
+  t_last_bwd = 1;
+  return (int)launch_general(1, a->prob.dtype, p, st);
+}
+
+int ab200_bwd_dq(const ab200_attn_bwd_args* a, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Params p{};
+  if (int e = fill_bwd(a, p, true)) return e;
+  if (!a->dq.ptr) return kErrInvalidValue;
+  if (int e = check_device(st)) return e;
+  const int family = g_family;
+  if (want_sm100(family) && sm100_bwd_supported(a->prob.dtype, p)) {
+    t_last_bwd = 2;
+    return (int)launch_sm100_bwd_dq(a->prob.dtype, p, st);
+  }
+  if (family == 2) return kErrNotSupported;
+  t_last_bwd = 1;
+  return (int)launch_general(2, a->prob.dtype, p, st);
+}
+
+int ab200_attn_bwd(const ab200_attn_bwd_args* a, void* stream) {
+  if (a == nullptr) return kErrInvalidValue;
+  if (!a->dq.ptr || !a->dk.ptr || !a->dv.ptr) return kErrInvalidValue;
+  if (int e = ab200_bwd_preprocess(a, stream)) return e;
+  if (int e = ab200_bwd_dkdv(a, stream)) return e;
+  return ab200_bwd_dq(a, stream);
+}
+
+// --- HIP-named runtime helpers used by the Python tests of the reference
+// (bindings/hipruntime.cc:92-93).  CUDA and HIP number their common errors alike.
+AB200_API int hipGetLastError(void) { return (int)cudaGetLastError(); }
+AB200_API int hipDeviceSynchronize(void) { return (int)cudaDeviceSynchronize(); }
+
+}  // extern "C"

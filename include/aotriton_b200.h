@@ -1,0 +1,164 @@
+/*
+ * aotriton_b200.h -- C-ABI of the B200 FlashAttention launcher.
+ *
+ * Everything the C++ operator API (include/aotriton/flash.h) and the Python
+ * bindings do on the device goes through the functions declared here.  The
+ * signatures use plain pointers, integers and POD structs only, so the same
+ * library can be bound from C, ctypes, cgo or any other FFI.
+ *
+ * Conventions
+ *   - Every pointer inside the structs is a DEVICE pointer unless stated.
+ *   - Strides are in ELEMENTS (not bytes), the innermost stride must be 1.
+ *   - Logical tensor order is (batch, head, sequence, head_dim) whatever the
+ *     storage order is; permuted storage (BSHD, THD) is expressed by strides.
+ *   - Return value: 0 on success, otherwise a HIP/CUDA-compatible error
+ *     number (see include/hip/hip_runtime.h for the names used).
+ *   - All launches are asynchronous on `stream` (a cudaStream_t passed as
+ *     void*; NULL is the default stream).  Nothing is allocated or freed.
+ *
+ * Each entry point cites the interface of ROCm/aotriton it stands in for.
+ */
+#ifndef AOTRITON_B200_CABI_H
+#define AOTRITON_B200_CABI_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_MSC_VER)
+#define AB200_API __declspec(dllexport)
+#else
+#define AB200_API __attribute__((visibility("default")))
+#endif
+
+/* Element types; numeric values equal aotriton::DType (include/aotriton/dtypes.h:12-25). */
+enum ab200_dtype {
+  AB200_DTYPE_UNKNOWN = 0,
+  AB200_DTYPE_FP32 = 1,
+  AB200_DTYPE_FP16 = 2,
+  AB200_DTYPE_BF16 = 3
+};
+
+/* causal_type values (include/aotriton/flash.h:76-81). */
+enum { AB200_CAUSAL_NONE = 0, AB200_CAUSAL_WINDOWED = 3 };
+/* window sentinels (include/aotriton/flash.h:83-86). */
+enum { AB200_WINDOW_TOP_LEFT = -2147483647, AB200_WINDOW_BOTTOM_RIGHT = -2147483646 };
+/* varlen_type values (include/aotriton/flash.h:88-93). */
+enum { AB200_VARLEN_NONE = 0, AB200_VARLEN_COMPACT = 1, AB200_VARLEN_PADDED = 2, AB200_VARLEN_STRIDED = 3 };
+
+/* A rank-4 strided view: logical (batch, head, seq, dim). ptr == NULL means "absent". */
+typedef struct ab200_view4 {
+  void* ptr;
+  int64_t stride[4];
+} ab200_view4;
+
+/*
+ * Problem description shared by forward and backward
+ * (fields of attn_fwd_params / attn_bwd_params, include/aotriton/flash.h:96-174,
+ * after the inference done in modules/flash/csrc/attn_fwd.cc:59-75).
+ */
+typedef struct ab200_attn_problem {
+  int32_t dtype;          /* ab200_dtype of Q/K/V/Out/bias and the gradients          */
+  int32_t batch;          /* dense: Q.size(0); varlen: number of sequences            */
+  int32_t num_head_q;
+  int32_t num_head_k;     /* num_head_q % num_head_k == 0 (GQA)                        */
+  int32_t max_seqlen_q;   /* dense: Q.size(2); varlen: Max_seqlen_q                    */
+  int32_t max_seqlen_k;
+  int32_t head_dim_qk;
+  int32_t head_dim_vo;
+  float sm_scale;
+  int32_t causal_type;    /* AB200_CAUSAL_*                                            */
+  int32_t window_left;    /* integers or AB200_WINDOW_* sentinels                      */
+  int32_t window_right;
+  int32_t varlen_type;    /* AB200_VARLEN_*                                            */
+  const int32_t* cu_seqlens_q;   /* batch+1 entries, NULL when dense                  */
+  const int32_t* cu_seqlens_k;
+  const int32_t* seq_strides_q;  /* strided varlen: batch+1 entries, else NULL         */
+  const int32_t* seq_strides_k;
+  float dropout_p;
+  const uint64_t* philox_seed;     /* device scalar, NULL -> 0                         */
+  const uint64_t* philox_offset1;  /* device scalar, NULL -> 0                         */
+  uint64_t philox_offset2;         /* host scalar added to *philox_offset1             */
+  /* Sharding support: when a caller splits the q-head axis over several GPUs it
+   * passes the position of this shard in the unsharded problem so that dropout
+   * masks stay identical.  0/0 means "not sharded". */
+  int32_t philox_head_offset;
+  int32_t philox_num_head_q;
+} ab200_attn_problem;
+
+/* Forward tensors (attn_fwd_params, include/aotriton/flash.h:96-130). */
+typedef struct ab200_attn_fwd_args {
+  ab200_attn_problem prob;
+  ab200_view4 q, k, v, bias, out;
+  float* lse;                       /* (batch*Hq, max_seqlen_q) or (Hq, total_q); may be NULL */
+  uint64_t* philox_seed_output;     /* may be NULL */
+  uint64_t* philox_offset_output;   /* may be NULL */
+  ab200_view4 encoded_softmax;      /* debugging aid, normally absent */
+  int32_t encoded_softmax_rows;     /* size(2) of encoded_softmax */
+  int32_t encoded_softmax_cols;     /* size(3) of encoded_softmax */
+  int32_t* persistent_atomic_counter; /* accepted for compatibility, never required */
+} ab200_attn_fwd_args;
+
+/* Backward tensors (attn_bwd_params, include/aotriton/flash.h:138-174). */
+typedef struct ab200_attn_bwd_args {
+  ab200_attn_problem prob;
+  ab200_view4 q, k, v, bias, out, dout;
+  ab200_view4 dq, dk, dv, dbias;    /* dbias absent or all-zero strides -> not written */
+  const float* lse;                 /* as written by the forward */
+  float* delta;                     /* scratch, same shape as lse (the "D" lazy tensor) */
+  int32_t deterministic;            /* attn_options::deterministic; results are always deterministic */
+} ab200_attn_bwd_args;
+
+/* Replaces aotriton::v3::flash::attn_fwd's launch (modules/flash/csrc/attn_fwd.cc:49-149). */
+AB200_API int ab200_attn_fwd(const ab200_attn_fwd_args* args, void* stream);
+
+/* Replaces aotriton::v3::flash::attn_bwd's three launches
+ * (modules/flash/csrc/attn_bwd.cc:56-160: bwd_preprocess, bwd_kernel_dk_dv, bwd_kernel_dq). */
+AB200_API int ab200_attn_bwd(const ab200_attn_bwd_args* args, void* stream);
+
+/* The three backward stages one by one (modules/flash/kernel/bwd_preprocess.py:28-250,
+ * bwd_kernel_dk_dv.py:48-417, bwd_kernel_dq.py:45-389). */
+AB200_API int ab200_bwd_preprocess(const ab200_attn_bwd_args* args, void* stream);
+AB200_API int ab200_bwd_dkdv(const ab200_attn_bwd_args* args, void* stream);
+AB200_API int ab200_bwd_dq(const ab200_attn_bwd_args* args, void* stream);
+
+/* Replaces aotriton::v2::flash::debug_simulate_encoded_softmax
+ * (modules/flash/csrc/attn_debug.cc:31-69, kernel/dropout_rng.py:86-126):
+ * r[b,h,m,n] = +0.5 where the Philox keep bit is set, -0.5 elsewhere. */
+AB200_API int ab200_debug_simulate_encoded_softmax(const ab200_view4* r, int32_t dtype,
+                                                   int32_t batch, int32_t num_head_q,
+                                                   int32_t rows, int32_t cols, float dropout_p,
+                                                   const uint64_t* philox_seed,
+                                                   const uint64_t* philox_offset1,
+                                                   uint64_t philox_offset2, void* stream);
+
+/* Replaces aotriton::v2::flash::check_gpu (modules/flash/csrc/attn_check.cc:36-46):
+ * 0 when the stream's device is an sm_100 part, hipErrorNoBinaryForGpu (209) otherwise. */
+AB200_API int ab200_check_gpu(void* stream);
+
+/* Replaces aotriton::getMultiProcessorCount (v3src/util.cc:77-112). */
+AB200_API int ab200_multiprocessor_count(void* stream);
+
+/* Selects the kernel family: 0 = automatic (tcgen05 kernels where they apply),
+ * 1 = force the general SIMT kernels, 2 = require tcgen05 kernels (unsupported
+ * shapes then return hipErrorNotSupported).  Counterpart of
+ * attn_options::force_backend_index (include/aotriton/flash.h:38-40).  Returns the old value. */
+AB200_API int ab200_set_kernel_family(int family);
+
+/* Which family the most recent forward / backward launch of this thread used
+ * (1 = general, 2 = tcgen05); diagnostics for tests and benchmarks. */
+AB200_API int ab200_last_fwd_family(void);
+AB200_API int ab200_last_bwd_family(void);
+
+/* Number of kernels launched by this library since load (all threads). */
+AB200_API uint64_t ab200_launch_count(void);
+
+/* Library version string, e.g. "aotriton_b200 0.1 (sm_100a)". */
+AB200_API const char* ab200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AOTRITON_B200_CABI_H */
