@@ -84,6 +84,7 @@ struct LazyHelper {
   };
   static aotriton::TensorView<Rank> acquire(aotriton::LazyTensor<Rank>* self) {
     auto* ctx = static_cast<Ctx*>(self->cookie);
+    if (!ctx) return aotriton::TensorView<Rank>();   // already disposed: a lazy tensor serves one call
     std::array<uint64_t, Rank> sizes = ctx->like.sizes(), strides{};
     uint64_t n = 1;
     for (int i = Rank - 1; i >= 0; --i) { strides[i] = n; n *= sizes[i]; }
