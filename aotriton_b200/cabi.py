@@ -20,13 +20,14 @@ VARLEN_NONE, VARLEN_COMPACT, VARLEN_PADDED, VARLEN_STRIDED = 0, 1, 2, 3
 SYMBOLS = [
     "ab200_attn_fwd", "ab200_attn_bwd", "ab200_bwd_preprocess", "ab200_bwd_dkdv", "ab200_bwd_dq",
     "ab200_debug_simulate_encoded_softmax", "ab200_check_gpu", "ab200_multiprocessor_count",
-    "ab200_set_kernel_family", "ab200_last_fwd_family", "ab200_last_bwd_family", "ab200_launch_count",
+    "ab200_set_kernel_family", "ab200_last_fwd_family", "ab200_last_bwd_family", "ab200_kernel_status",
+    "ab200_launch_count",
     "ab200_version",
 ]
 
 
 class View4(C.Structure):
-    _fields_ = [("ptr", C.c_void_p), ("stride", C.c_int64 * 4)]
+    _fields_ = [("ptr", C.c_void_p), ("size", C.c_int64 * 4), ("stride", C.c_int64 * 4)]
 
 
 class Problem(C.Structure):
@@ -79,6 +80,8 @@ def lib() -> C.CDLL:
         L.ab200_check_gpu.argtypes = [C.c_void_p]
         L.ab200_multiprocessor_count.argtypes = [C.c_void_p]
         L.ab200_set_kernel_family.argtypes = [C.c_int]
+        L.ab200_kernel_status.argtypes = [C.c_int]
+        L.ab200_kernel_status.restype = C.c_uint
         L.ab200_launch_count.restype = C.c_uint64
         L.ab200_version.restype = C.c_char_p
         _lib = L
@@ -98,6 +101,7 @@ def view4(t) -> View4:
     assert t.dim() == 4
     v.ptr = t.data_ptr()
     for i in range(4):
+        v.size[i] = t.shape[i]
         v.stride[i] = t.stride(i)
     return v
 

@@ -46,7 +46,10 @@ void log_debug(const char* fmt, ...) {
 ab200_view4 cview(const TensorView<4>& t) {
   ab200_view4 v;
   v.ptr = t.data_ptr();
-  for (int i = 0; i < 4; ++i) v.stride[i] = t ? (int64_t)t.stride(i) : 0;
+  for (int i = 0; i < 4; ++i) {
+    v.size[i] = t ? (int64_t)t.size(i) : 0;
+    v.stride[i] = t ? (int64_t)t.stride(i) : 0;
+  }
   return v;
 }
 

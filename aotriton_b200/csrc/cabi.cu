@@ -70,7 +70,7 @@ int check_device(cudaStream_t st) {
 
 View4 to_view(const ab200_view4& v) {
   View4 r; r.ptr = v.ptr;
-  for (int i = 0; i < 4; ++i) r.s[i] = v.stride[i];
+  for (int i = 0; i < 4; ++i) { r.n[i] = v.size[i]; r.s[i] = v.stride[i]; }
   return r;
 }
 
@@ -132,6 +132,7 @@ int ab200_set_kernel_family(int family) {
 }
 int ab200_last_fwd_family(void) { return t_last_fwd; }
 int ab200_last_bwd_family(void) { return t_last_bwd; }
+unsigned int ab200_kernel_status(int reset) { return sm100_read_status(reset != 0); }
 uint64_t ab200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 const char* ab200_version(void) { return "aotriton_b200 0.1 (sm_100a; API level of aotriton 0.14)"; }
 

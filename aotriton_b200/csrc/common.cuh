@@ -23,7 +23,8 @@ constexpr float kLn2 = 0.6931471824645996f;
 
 struct View4 {
   void* ptr;
-  int64_t s[4];
+  int64_t n[4];   // extents
+  int64_t s[4];   // strides in elements
 };
 
 // Everything a kernel needs, passed by value as a __grid_constant__ parameter.

@@ -1,5 +1,445 @@
+// Forward attention on the 5th-generation tensor cores (tcgen05) of sm_100a.
+//
+// One CTA owns a tile of 128 query rows of one (sequence, q-head) and walks the key/value
+// blocks (128 keys each) its window can reach.  Six warps, three roles:
+//
+//   warp 0      TMA producer   Q once, then K and V blocks through two 2-stage rings
+//                              (cp.async.bulk.tensor, 128-byte swizzle, this CTA only)
+//   warp 1      MMA issuer     one elected thread issues  S = Q K^T  (both operands in
+//                              shared memory) into one of two S buffers in tensor memory and
+//                              O += P V  (P read straight from tensor memory, V from shared
+//                              memory, N-major); completion is signalled with tcgen05.commit
+//   warps 2-5   softmax        thread r owns query row r: tcgen05.ld of the S row, scale,
+//                              bias, mask, running max / sum in the exp2 domain, dropout,
+//                              P written back over S as packed 16-bit, lazy rescale of O,
+//                              final normalisation, O and LSE stores
+//
+// Tensor memory (512 columns): S0 [0,128)  S1 [128,256)  O [256, 256+HD).  P_j aliases the
+// first 64 columns of S_{j%2}.  S_{j+1} is computed while the softmax warps work on S_j.
+//
+// Arithmetic contract (ROCm/aotriton modules/flash/kernel/fwd_kernel_inner.py:126-277,
+// fwd_kernel.py:573-620): logits scaled by sm_scale*log2(e), bias*log2(e) added, masked
+// scores -inf, row sum taken BEFORE dropout, P cast to the value dtype before P V,
+// O = acc / l / (1-p), LSE = (m + log2 l) * ln2, rows that see no key give O = 0, LSE = +inf.
+// The running maximum is only advanced when it grows by more than 8 (a factor 256 in P);
+// the result is the same function of the inputs, with fewer passes over O.
+//
+// Every wait is bounded (sm100_ptx.cuh); on a time-out the CTA drains and exits, and the
+// word behind `status` records which wait gave up.
 #include "launch.h"
+#include "sm100_ptx.cuh"
+
 namespace ab200 {
-bool sm100_fwd_supported(int, const Params&) { return false; }
-cudaError_t launch_sm100_fwd(int, const Params&, cudaStream_t) { return cudaErrorNotSupported; }
+
+__device__ unsigned int g_sm100_status = 0;
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128, kBN = 128, kStages = 2;
+constexpr int kFwdThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;
+
+template <int HD>
+struct FwdSmem {
+  static constexpr int kHalves = HD / 64;
+  static constexpr int kTileBytes = kHalves * 128 * 128;     // 128 rows x HD x 2 bytes
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kTileBytes;
+  static constexpr int kV = kK + kStages * kTileBytes;
+  static constexpr int kBars = kV + kStages * kTileBytes;
+  // barrier slots (8 bytes each)
+  static constexpr int bQFull = 0, bKFull = 1, bKEmpty = 3, bVFull = 5, bVEmpty = 7, bSFull = 9, bPFull = 11,
+                       bPvDone = 13, bCount = 14;
+  static constexpr int kTmemSlot = kBars + bCount * 8;
+  static constexpr int kAbort = kTmemSlot + 4;
+  static constexpr int kTotal = kAbort + 4;
+  static constexpr int kDynamic = kTotal + 1024;             // slack for manual 1024-byte alignment
+};
+
+template <typename T> struct Fmt;
+template <> struct Fmt<__half> { static constexpr uint32_t code = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t code = 1; };
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
 }
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Rows of the tile that have no key at all: O = 0, LSE = +inf.
+template <typename T>
+__device__ void write_dead_tile(const Params& p, const Seq& sq, int h, int m0) {
+  for (int r = threadIdx.x; r < kBM; r += blockDim.x) {
+    int m = m0 + r;
+    if (m >= sq.sq) continue;
+    T* op = reinterpret_cast<T*>(p.out.ptr) + (int64_t)sq.bidx * p.out.s[0] + (int64_t)h * p.out.s[1] +
+            (sq.q0 + m) * p.out.s[2];
+    for (int d = 0; d < p.dvo; ++d) op[d] = from_f32<T>(0.f);
+    if (p.lse) p.lse[lse_offset(p, sq, h) + m] = INFINITY;
+  }
+}
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tm_q,
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                 unsigned int* status) {
+  using L = FwdSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAbort);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int z = blockIdx.z, h = blockIdx.y;
+  const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * kBM;     // long tiles of a causal problem first
+  if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;   // an earlier CTA timed out
+  const Seq sq = resolve_seq(p, z);
+  if (m0 >= sq.sq) return;
+  const int hk = h / p.group;
+
+  if (p.dropout_on && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+    uint64_t seed = p.seed_ptr ? *p.seed_ptr : 0ull;
+    uint64_t base = p.off2 + (p.off1_ptr ? *p.off1_ptr : 0ull);
+    if (p.seed_out) *p.seed_out = seed;
+    if (p.off_out) *p.off_out = base;
+  }
+
+  int n_lo, n_hi;
+  key_range(p, sq, m0, min(m0 + kBM, sq.sq) - 1, n_lo, n_hi);
+  if (n_hi < n_lo) {            // CTA-uniform: nothing to attend to
+    write_dead_tile<T>(p, sq, h, m0);
+    return;
+  }
+  const int jb_lo = n_lo / kBN;
+  const int nblk = n_hi / kBN - jb_lo + 1;
+
+  // ---- set-up -----------------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(&bars[L::bQFull], 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars[L::bKFull + s], 1);
+      mbar_init(&bars[L::bKEmpty + s], 1);
+      mbar_init(&bars[L::bVFull + s], 1);
+      mbar_init(&bars[L::bVEmpty + s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars[L::bSFull + s], 1);
+      mbar_init(&bars[L::bPFull + s], 128);
+    }
+    mbar_init(&bars[L::bPvDone], 1);
+    fence_barrier_init();
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 256;
+
+  if (warp == 0) {
+    // =============================== TMA producer ===================================
+    if (lane == 0) {
+      const int qrow = (int)(sq.q0 + m0);
+      mbar_expect_tx(&bars[L::bQFull], L::kTileBytes);
+      for (int hf = 0; hf < L::kHalves; ++hf)
+        tma_load_4d(smem + L::kQ + hf * 16384, &tm_q, &bars[L::bQFull], hf * 64, qrow, h, sq.bidx);
+      int issued = 0;
+      for (int j = 0; j < nblk; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (uint32_t)(j / kStages) & 1u;
+        const int krow = (int)(sq.k0 + (int64_t)(jb_lo + j) * kBN);
+        if (!mbar_wait(&bars[L::bKEmpty + s], ph ^ 1u, abort_flag, status, 0x100 + j)) break;
+        mbar_expect_tx(&bars[L::bKFull + s], L::kTileBytes);
+        for (int hf = 0; hf < L::kHalves; ++hf)
+          tma_load_4d(smem + L::kK + s * L::kTileBytes + hf * 16384, &tm_k, &bars[L::bKFull + s], hf * 64, krow, hk,
+                      sq.bidx);
+        if (!mbar_wait(&bars[L::bVEmpty + s], ph ^ 1u, abort_flag, status, 0x200 + j)) { issued = j * 2 + 1; break; }
+        mbar_expect_tx(&bars[L::bVFull + s], L::kTileBytes);
+        for (int hf = 0; hf < L::kHalves; ++hf)
+          tma_load_4d(smem + L::kV + s * L::kTileBytes + hf * 16384, &tm_v, &bars[L::bVFull + s], hf * 64, krow, hk,
+                      sq.bidx);
+        issued = j * 2 + 2;
+      }
+      if (*abort_flag) {
+        // Let copies that are still in flight land before the CTA gives its shared memory back.
+        mbar_wait_quiet(&bars[L::bQFull], 0);
+        for (int i = max(0, issued - 2 * kStages); i < issued; ++i) {
+          int j = i >> 1, s = j % kStages;
+          uint32_t ph = (uint32_t)(j / kStages) & 1u;
+          mbar_wait_quiet((i & 1) ? &bars[L::bVFull + s] : &bars[L::bKFull + s], ph);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ================================ MMA issuer ====================================
+    if (lane == 0) {
+      constexpr uint32_t kIdescQK = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
+      constexpr uint32_t kIdescPV = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
+      const uint32_t q_addr = smem_u32(smem + L::kQ);
+      const uint32_t k_addr = smem_u32(smem + L::kK);
+      const uint32_t v_addr = smem_u32(smem + L::kV);
+      bool ok = mbar_wait(&bars[L::bQFull], 0, abort_flag, status, 0x300);
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j % kStages;
+        if (!mbar_wait(&bars[L::bKFull + s], (uint32_t)(j / kStages) & 1u, abort_flag, status, 0x400 + j)) return false;
+        tc_fence_after();
+        const uint32_t d = tmem_base + (uint32_t)(j & 1) * 128u;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u;
+          mma_ss(d, smem_desc_sw128(q_addr + off, 16, 1024),
+                 smem_desc_sw128(k_addr + (uint32_t)s * L::kTileBytes + off, 16, 1024), kIdescQK, kk > 0);
+        }
+        mma_commit(&bars[L::bKEmpty + s]);
+        mma_commit(&bars[L::bSFull + (j & 1)]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; ok && j < nblk; ++j) {
+        if (j + 1 < nblk) {
+          if (!issue_qk(j + 1)) break;
+        }
+        const int s = j % kStages;
+        if (!mbar_wait(&bars[L::bPFull + (j & 1)], (uint32_t)(j >> 1) & 1u, abort_flag, status, 0x500 + j)) break;
+        if (!mbar_wait(&bars[L::bVFull + s], (uint32_t)(j / kStages) & 1u, abort_flag, status, 0x600 + j)) break;
+        tc_fence_after();
+        const uint32_t pcol = tmem_base + (uint32_t)(j & 1) * 128u;
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk) {
+          // 16 keys per step: 8 packed columns of P, 2048 bytes of V (two 8-key groups)
+          mma_ts(tmem_o, pcol + (uint32_t)kk * 8u,
+                 smem_desc_sw128(v_addr + (uint32_t)s * L::kTileBytes + (uint32_t)kk * 2048u, 16384, 1024), kIdescPV,
+                 (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(&bars[L::bVEmpty + s]);
+        mma_commit(&bars[L::bPvDone]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ================================== softmax =====================================
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int m = m0 + r;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    int row_lo = 0, row_hi = sq.sk - 1;
+    if (p.causal) {
+      int64_t lo = (int64_t)m - sq.wl, hi = (int64_t)m + sq.wr;
+      if (lo > row_lo) row_lo = (int)(lo > 0x7fffffffLL ? 0x7fffffffLL : lo);
+      if (hi < row_hi) row_hi = (int)(hi < -1 ? -1 : hi);
+    }
+    if (m >= sq.sq) { row_lo = 1; row_hi = 0; }
+    DropoutCtx dctx;
+    if (p.dropout_on) dctx = dropout_ctx(p, z, h);
+    const T* bias_row = nullptr;
+    if (p.has_bias)
+      bias_row = reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] + (int64_t)h * p.bias.s[1] +
+                 (int64_t)min(m, sq.sq - 1) * p.bias.s[2];
+
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblk; ++j) {
+      const int n0 = (jb_lo + j) * kBN;
+      const int sb = j & 1;
+      if (!mbar_wait(&bars[L::bSFull + sb], (uint32_t)(j >> 1) & 1u, abort_flag, status, 0x700 + j)) { ok = false; break; }
+      tc_fence_after();
+      float sc[128];
+      const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)sb * 128u;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32f(s_addr + c * 32, &sc[c * 32]);
+      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 128; ++c) sc[c] *= p.qk_scale;
+      if (p.has_bias) {
+        const int nmax = sq.sk - n0;
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if (c < nmax) sc[c] = fmaf(to_f32<T>(bias_row[(int64_t)(n0 + c) * p.bias.s[3]]), kLog2e, sc[c]);
+      }
+      const bool need_mask = !(n0 >= row_lo && n0 + kBN - 1 <= row_hi);
+      if (__any_sync(0xffffffffu, need_mask)) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          const int n = n0 + c;
+          sc[c] = (n >= row_lo && n <= row_hi) ? sc[c] : -INFINITY;
+        }
+      }
+      float mx = sc[0];
+#pragma unroll
+      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, sc[c]);
+      // Advance the reference maximum only when it moved by more than the threshold.
+      const bool grow = mx > m_used + kRescaleThreshold;     // false when mx == -inf
+      float alpha = 1.f;
+      if (grow) {
+        alpha = exp2f(m_used - mx);                          // m_used == -inf -> 0
+        m_used = mx;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        // O must be complete up to block j-1 before it is rescaled.
+        if (!mbar_wait(&bars[L::bPvDone], (uint32_t)(j - 1) & 1u, abort_flag, status, 0x800 + j)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tmem_o + lane_addr + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tmem_o + lane_addr + c * 32, o);
+        }
+        tmem_wait_st();
+      }
+      l *= alpha;
+      const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 128; ++c) {
+        sc[c] = exp2f(sc[c] - m_safe);
+        sum += sc[c];
+      }
+      l += sum;
+      if (p.dropout_on) {
+        const int mm = min(m, p.max_sq - 1);
+#pragma unroll
+        for (int c4 = 0; c4 < 32; ++c4) {
+          const uint32_t keep = dropout_keep4(dctx, mm, (n0 >> 2) + c4);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (!((keep >> i) & 1u)) sc[c4 * 4 + i] = 0.f;
+        }
+      }
+      // P over the first 64 columns of this S buffer, two 16-bit values per column.
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(sc[c * 32 + 2 * i], sc[c * 32 + 2 * i + 1]);
+        tmem_st16(s_addr + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bars[L::bPFull + sb]);
+    }
+    // ---- epilogue ---------------------------------------------------------------------
+    if (ok) ok = mbar_wait(&bars[L::bPvDone], (uint32_t)(nblk - 1) & 1u, abort_flag, status, 0x900);
+    if (ok) {
+      tc_fence_after();
+      const float inv = (l > 0.f) ? p.dropout_scale / l : 0.f;
+      T* op = reinterpret_cast<T*>(p.out.ptr) + (int64_t)sq.bidx * p.out.s[0] + (int64_t)h * p.out.s[1] +
+              (sq.q0 + m) * p.out.s[2];
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tmem_o + lane_addr + c * 32, o);
+        tmem_wait_ld();
+        if (m < sq.sq) {
+#pragma unroll
+          for (int v8 = 0; v8 < 4; ++v8) {
+            const int d = c * 32 + v8 * 8;
+            if (d < p.dvo) {
+              uint4 w;
+              w.x = pack2<T>(__uint_as_float(o[v8 * 8 + 0]) * inv, __uint_as_float(o[v8 * 8 + 1]) * inv);
+              w.y = pack2<T>(__uint_as_float(o[v8 * 8 + 2]) * inv, __uint_as_float(o[v8 * 8 + 3]) * inv);
+              w.z = pack2<T>(__uint_as_float(o[v8 * 8 + 4]) * inv, __uint_as_float(o[v8 * 8 + 5]) * inv);
+              w.w = pack2<T>(__uint_as_float(o[v8 * 8 + 6]) * inv, __uint_as_float(o[v8 * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(op + d) = w;
+            }
+          }
+        }
+      }
+      if (p.lse != nullptr && m < sq.sq)
+        p.lse[lse_offset(p, sq, h) + m] = (l > 0.f) ? (m_used + log2f(l)) * kLn2 : INFINITY;
+    }
+  }
+
+  // ---- tear-down ------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
+
+bool tma_friendly(const View4& v) {
+  if (!aligned16(v.ptr)) return false;
+  for (int i = 0; i < 3; ++i)
+    if (v.n[i] > 1 && (v.s[i] % 8 != 0 || v.s[i] <= 0)) return false;
+  for (int i = 0; i < 4; ++i)
+    if (v.n[i] <= 0 || v.n[i] > 0x7fffffffLL) return false;
+  return v.s[3] == 1;
+}
+
+template <typename T, int HD>
+cudaError_t launch_fwd_T(const Params& p, cudaStream_t st) {
+  using L = FwdSmem<HD>;
+  CUtensorMap tq, tk, tv;
+  if (!make_tile_map_16bit(&tq, p.q, p.dqk, p.q.n[2], kBM) || !make_tile_map_16bit(&tk, p.k, p.dqk, p.k.n[2], kBN) ||
+      !make_tile_map_16bit(&tv, p.v, p.dvo, p.v.n[2], kBN))
+    return cudaErrorInvalidValue;
+  // The attribute belongs to the (function, device) pair; setting it on every launch keeps
+  // multi-device processes correct and costs microseconds.
+  cudaError_t e = cudaFuncSetAttribute(sm100_fwd_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       L::kDynamic);
+  if (e != cudaSuccess) return e;
+  unsigned int* status = nullptr;
+  e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_sm100_status);
+  if (e != cudaSuccess) return e;
+  dim3 grid((p.max_sq + kBM - 1) / kBM, p.hq, p.batch);
+  sm100_fwd_kernel<T, HD><<<grid, kFwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, status);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool sm100_fwd_supported(int dtype, const Params& p) {
+  if (dtype != 2 && dtype != 3) return false;                    // fp16 / bf16 only
+  if (p.dqk > 128 || p.dvo > 128 || p.dqk % 8 != 0 || p.dvo % 8 != 0) return false;
+  if (p.max_sq <= 0 || p.max_sk <= 0 || p.batch <= 0) return false;
+  if (!tma_friendly(p.q) || !tma_friendly(p.k) || !tma_friendly(p.v)) return false;
+  // O is written with 16-byte vector stores
+  if (!aligned16(p.out.ptr) || p.out.s[0] % 8 != 0 || p.out.s[1] % 8 != 0 || p.out.s[2] % 8 != 0) return false;
+  if (p.q.n[3] != p.dqk || p.k.n[3] != p.dqk || p.v.n[3] != p.dvo) return false;
+  return tensor_map_encoder() != nullptr;
+}
+
+cudaError_t launch_sm100_fwd(int dtype, const Params& p, cudaStream_t st) {
+  const bool small = p.dqk <= 64 && p.dvo <= 64;
+  if (dtype == 2) return small ? launch_fwd_T<__half, 64>(p, st) : launch_fwd_T<__half, 128>(p, st);
+  return small ? launch_fwd_T<__nv_bfloat16, 64>(p, st) : launch_fwd_T<__nv_bfloat16, 128>(p, st);
+}
+
+unsigned int sm100_read_status(bool reset) {
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_sm100_status, sizeof(v)) != cudaSuccess) { (void)cudaGetLastError(); return 0xffffffffu; }
+  if (reset && v != 0) {
+    unsigned int zero = 0;
+    if (cudaMemcpyToSymbol(g_sm100_status, &zero, sizeof(zero)) != cudaSuccess) (void)cudaGetLastError();
+  }
+  return v;
+}
+
+}  // namespace ab200

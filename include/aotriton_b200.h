@@ -48,9 +48,13 @@ enum { AB200_WINDOW_TOP_LEFT = -2147483647, AB200_WINDOW_BOTTOM_RIGHT = -2147483
 /* varlen_type values (include/aotriton/flash.h:88-93). */
 enum { AB200_VARLEN_NONE = 0, AB200_VARLEN_COMPACT = 1, AB200_VARLEN_PADDED = 2, AB200_VARLEN_STRIDED = 3 };
 
-/* A rank-4 strided view: logical (batch, head, seq, dim). ptr == NULL means "absent". */
+/* A rank-4 strided view: logical (batch, head, seq, dim). ptr == NULL means "absent".
+ * size[] are the extents of the tensor the view was taken from (for compact varlen the
+ * sequence extent is the total token count); the tcgen05 kernels bound their bulk
+ * copies with them. */
 typedef struct ab200_view4 {
   void* ptr;
+  int64_t size[4];
   int64_t stride[4];
 } ab200_view4;
 
@@ -151,6 +155,12 @@ AB200_API int ab200_set_kernel_family(int family);
  * (1 = general, 2 = tcgen05); diagnostics for tests and benchmarks. */
 AB200_API int ab200_last_fwd_family(void);
 AB200_API int ab200_last_bwd_family(void);
+
+/* Health word of the tcgen05 kernels on the current device: 0, or a code naming the
+ * bounded wait that ran out (the kernels never spin forever; they give up after about a
+ * second, record where, and exit).  Synchronises the device.  reset != 0 clears the word.
+ * The reference has no counterpart: its kernels contain no waits. */
+AB200_API unsigned int ab200_kernel_status(int reset);
 
 /* Number of kernels launched by this library since load (all threads). */
 AB200_API uint64_t ab200_launch_count(void);

@@ -98,6 +98,7 @@ def test_cabi_rejects_null_and_bad_strides():
     for v in (a.q, a.k, a.v, a.out):
         v.ptr = 0x1000
         v.stride[0], v.stride[1], v.stride[2], v.stride[3] = 4096, 1024, 64, 2
+        v.size[0], v.size[1], v.size[2], v.size[3] = 1, 4, 16, 64
     assert cabi.lib().ab200_attn_fwd(a, None) == 1                          # innermost stride must be 1
     a.prob.dropout_p = 1.5
     assert cabi.lib().ab200_attn_fwd(a, None) == 1
