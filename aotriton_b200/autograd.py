@@ -58,11 +58,12 @@ class _Attention(torch.autograd.Function):
         return dq, dk, dv, db, None, None, None, None, None, None
 
 
-def attention(q, k, v, b=None, causal=False, sm_scale=None, dropout_p=0.0, return_lse=False, **kw):
+def attention(q, k, v, b=None, causal=False, sm_scale=None, dropout_p=0.0, return_lse=False,
+              philox_seed=DEFAULT_PHILOX_SEED, philox_offset1=DEFAULT_PHILOX_OFFSET_1):
     """O = dropout(softmax(Q K^T * sm_scale + b, mask)) V for (B, H, S, D) tensors (any strides with
     unit innermost stride).  `causal` is a bool, a (left, right) window or a flash.CausalType."""
     sm_scale = q.shape[-1] ** -0.5 if sm_scale is None else sm_scale
-    return _Attention.apply(q, k, v, b, causal, sm_scale, dropout_p, return_lse, *kw.values())
+    return _Attention.apply(q, k, v, b, causal, sm_scale, dropout_p, return_lse, philox_seed, philox_offset1)
 
 
 class _VarlenAttention(torch.autograd.Function):
