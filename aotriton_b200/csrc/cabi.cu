@@ -132,7 +132,10 @@ int ab200_set_kernel_family(int family) {
 }
 int ab200_last_fwd_family(void) { return t_last_fwd; }
 int ab200_last_bwd_family(void) { return t_last_bwd; }
-unsigned int ab200_kernel_status(int reset) { return sm100_read_status(reset != 0); }
+unsigned int ab200_kernel_status(int reset) {
+  unsigned int f = sm100_fwd_status(reset != 0), b = sm100_bwd_status(reset != 0);
+  return f ? f : b;
+}
 uint64_t ab200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 const char* ab200_version(void) { return "aotriton_b200 0.1 (sm_100a; API level of aotriton 0.14)"; }
 

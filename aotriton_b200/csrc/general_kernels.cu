@@ -86,17 +86,18 @@ __global__ void __launch_bounds__(kThreads) general_fwd_kernel(const __grid_cons
   float* l_s = alpha_s + kTile;        // [16]
 
   const int z = blockIdx.z, h = blockIdx.y, m0 = blockIdx.x * kTile;
-  const Seq sq = resolve_seq(p, z);
-  if (m0 >= sq.sq) return;
-  const int hk = h / p.group;
-  const int tid = threadIdx.x, r = tid >> 4, c = tid & 15, warp = tid >> 5, lane = tid & 31;
-
-  if (p.dropout_on && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) {
+  // One thread of the grid reports the seed and offset actually used, before any early exit
+  // (the first sequence of a varlen batch may be empty).
+  if (p.dropout_on && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
     uint64_t seed = p.seed_ptr ? *p.seed_ptr : 0ull;
     uint64_t base = p.off2 + (p.off1_ptr ? *p.off1_ptr : 0ull);
     if (p.seed_out) *p.seed_out = seed;
     if (p.off_out) *p.off_out = base;
   }
+  const Seq sq = resolve_seq(p, z);
+  if (m0 >= sq.sq) return;
+  const int hk = h / p.group;
+  const int tid = threadIdx.x, r = tid >> 4, c = tid & 15, warp = tid >> 5, lane = tid & 31;
   DropoutCtx dctx;
   if (p.dropout_on) dctx = dropout_ctx(p, z, h);
 

@@ -35,8 +35,9 @@ cudaError_t launch_sm100_fwd(int dtype, const Params& p, cudaStream_t st);
 bool sm100_bwd_supported(int dtype, const Params& p);
 cudaError_t launch_sm100_bwd_dkdv(int dtype, const Params& p, cudaStream_t st);
 cudaError_t launch_sm100_bwd_dq(int dtype, const Params& p, cudaStream_t st);
-// Word the tcgen05 kernels of the current device set when a bounded wait ran out (0 = none).
-// Synchronises the device.
-unsigned int sm100_read_status(bool reset);
+// Words the tcgen05 kernels of the current device set when a bounded wait ran out (0 = none).
+// Reading synchronises the device.
+unsigned int sm100_fwd_status(bool reset);
+unsigned int sm100_bwd_status(bool reset);
 
 }  // namespace ab200

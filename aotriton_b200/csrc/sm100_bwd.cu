@@ -1,6 +1,723 @@
+// Backward attention on tcgen05 (sm_100a): the dK/dV kernel and the dQ(+dBias) kernel.
+// (delta = rowsum(O * dO) is produced beforehand by the streaming preprocess kernel.)
+//
+// Both kernels recompute the probabilities from Q, K and the forward's logsumexp and share
+// one scheme.  A CTA owns 128 rows of its output (keys for dK/dV, queries for dQ) and walks
+// 128-wide blocks of the other sequence dimension.  Twelve warps:
+//
+//   warp 0      TMA producer   resident operand pair once, then the streamed pair through a
+//                              2-stage ring (cp.async.bulk.tensor, 128-byte swizzle)
+//   warp 1      MMA issuer     one thread issues all tcgen05.mma and tcgen05.commit
+//   warp 2      (dK/dV only)   stages logsumexp*log2(e) and delta of the streamed query
+//                              block in shared memory
+//   warps 4-11  compute        thread = one output row of the 128x128 score tile (TMEM lane),
+//                              the two warpgroups split its columns 0-63 / 64-127
+//
+//   dK/dV, per query block i:   S^T = K Q_i^T      dP^T = V dO_i^T        (operands in smem)
+//                               P^T, dS^T computed in registers, written back over S^T / dP^T
+//                               as packed 16-bit
+//                               dV += P^T dO_i     dK += dS^T Q_i         (A from TMEM)
+//   dQ, per key block i:        S = Q K_i^T        dP = dO V_i^T
+//                               dQ += dS K_i       dB = dS
+//
+// Tensor memory: [0,128) S / P, [128,256) dP / dS, [256,384) dV or dQ, [384,512) dK.
+// A warpgroup writes its packed 16-bit results into the first half of ITS OWN column range
+// (columns it has already read), so the two warpgroups never overwrite each other's input;
+// the MMA issuer addresses the two halves separately.
+//
+// Arithmetic contract (ROCm/aotriton modules/flash/kernel/bwd_inner_dk_dv.py:117-256,
+// bwd_inner_dq.py:117-205, bwd_kernel_dk_dv.py:387-391, bwd_kernel_dq.py:374-376):
+//   P = exp2(qk_scale * QK^T + bias*log2e - LSE*log2e), 0 where masked;
+//   dP = dO V^T, with dropout: keep ? dP/(1-p) : 0;   dS = P * (dP - delta) with the un-dropped P;
+//   dV += cast(keep ? P/(1-p) : 0)^T dO;  dK += cast(dS)^T Q;  dQ += cast(dS) K;  dB = cast(dS);
+//   dK and dQ are multiplied by sm_scale at the end.
+//
+// Every wait is bounded (sm100_ptx.cuh).
 #include "launch.h"
+#include "sm100_ptx.cuh"
+
 namespace ab200 {
-bool sm100_bwd_supported(int, const Params&) { return false; }
-cudaError_t launch_sm100_bwd_dkdv(int, const Params&, cudaStream_t) { return cudaErrorNotSupported; }
-cudaError_t launch_sm100_bwd_dq(int, const Params&, cudaStream_t) { return cudaErrorNotSupported; }
+
+__device__ unsigned int g_sm100_bwd_status = 0;
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kBlk = 128;
+constexpr int kBwdThreads = 384;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 384;
+
+template <int HD>
+struct BwdSmem {
+  static constexpr int kHalves = HD / 64;
+  static constexpr int kTile = kHalves * 16384;          // 128 rows x HD x 2 bytes
+  static constexpr int kResA = 0, kResB = kTile;         // resident pair
+  static constexpr int kRingA = 2 * kTile, kRingB = 4 * kTile;   // two stages each
+  static constexpr int kAux = 6 * kTile;                 // 2 stages x (128 lse2 + 128 delta) floats
+  static constexpr int kBars = kAux + 2 * 256 * 4;
+  static constexpr int bResFull = 0, bRingFull = 1, bRingEmpty = 3, bAuxFull = 5, bAuxEmpty = 7, bSFull = 9,
+                       bDpFull = 10, bPFull = 11, bDsFull = 12, bAccDone = 13, bSRead = 14, bCount = 15;
+  static constexpr int kTmemSlot = kBars + bCount * 8;
+  static constexpr int kAbort = kTmemSlot + 4;
+  static constexpr int kDynamic = kAbort + 4 + 1024;
+};
+
+// K-major view of a [128 x HD] tile: k-step kk covers head-dim columns 16kk..16kk+15.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int kk) {
+  return smem_desc_sw128(tile_addr + (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u, 16, 1024);
 }
+// MN-major view of the same tile: k-step kk covers rows 16kk..16kk+15, N runs over the head dim.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int kk) {
+  return smem_desc_sw128(tile_addr + (uint32_t)kk * 2048u, 16384, 1024);
+}
+// Column of the packed 16-bit A operand for k-step kk when two warpgroups each packed their
+// 64 source columns into the first 32 columns of their own half.
+__device__ __forceinline__ uint32_t split_a_col(int kk) { return (uint32_t)((kk < 4) ? kk * 8 : 64 + (kk - 4) * 8); }
+
+template <typename T>
+__device__ __forceinline__ void store_row_chunk32(T* dst, const float* v, float scale, int d0, int dmax) {
+#pragma unroll
+  for (int v8 = 0; v8 < 4; ++v8) {
+    const int d = d0 + v8 * 8;
+    if (d < dmax) {
+      uint4 w;
+      w.x = pack2<T>(v[v8 * 8 + 0] * scale, v[v8 * 8 + 1] * scale);
+      w.y = pack2<T>(v[v8 * 8 + 2] * scale, v[v8 * 8 + 3] * scale);
+      w.z = pack2<T>(v[v8 * 8 + 4] * scale, v[v8 * 8 + 5] * scale);
+      w.w = pack2<T>(v[v8 * 8 + 6] * scale, v[v8 * 8 + 7] * scale);
+      *reinterpret_cast<uint4*>(dst + d) = w;
+    }
+  }
+}
+
+template <typename T>
+__device__ void zero_rows(const View4& v, int b, int h, int64_t tok0, int row0, int nrows, int d) {
+  for (int r = threadIdx.x; r < kBlk; r += blockDim.x) {
+    if (row0 + r >= nrows) continue;
+    T* ptr = reinterpret_cast<T*>(v.ptr) + (int64_t)b * v.s[0] + (int64_t)h * v.s[1] + (tok0 + row0 + r) * v.s[2];
+    for (int c = 0; c < d; ++c) ptr[c] = from_f32<T>(0.f);
+  }
+}
+
+template <int HD>
+__device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t* abort_flag) {
+  using L = BwdSmem<HD>;
+  *abort_flag = 0;
+  mbar_init(&bars[L::bResFull], 1);
+  for (int s = 0; s < 2; ++s) {
+    mbar_init(&bars[L::bRingFull + s], 1);
+    mbar_init(&bars[L::bRingEmpty + s], 1);
+    mbar_init(&bars[L::bAuxFull + s], 32);
+    mbar_init(&bars[L::bAuxEmpty + s], 256);
+  }
+  mbar_init(&bars[L::bSFull], 1);
+  mbar_init(&bars[L::bDpFull], 1);
+  mbar_init(&bars[L::bPFull], 256);
+  mbar_init(&bars[L::bDsFull], 256);
+  mbar_init(&bars[L::bAccDone], 1);
+  mbar_init(&bars[L::bSRead], 256);
+  fence_barrier_init();
+}
+
+// =========================================================================================
+// dK / dV.  grid = (cdiv(max_sk, 128), Hk, batch)
+template <typename T, int HD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tm_q,
+                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                      const __grid_constant__ CUtensorMap tm_do, unsigned int* status) {
+  using L = BwdSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAbort);
+  float* aux = reinterpret_cast<float*>(smem + L::kAux);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int z = blockIdx.z, hk = blockIdx.y, n0 = blockIdx.x * kBlk;
+  if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
+  const Seq sq = resolve_seq(p, z);
+  if (n0 >= sq.sk) return;
+  int m_lo, m_hi;
+  query_range(p, sq, n0, min(n0 + kBlk, sq.sk) - 1, m_lo, m_hi);
+  if (m_hi < m_lo) {   // no query attends to these keys
+    zero_rows<T>(p.dk, sq.bidx, hk, sq.k0, n0, sq.sk, p.dqk);
+    zero_rows<T>(p.dv, sq.bidx, hk, sq.k0, n0, sq.sk, p.dvo);
+    return;
+  }
+  const int mb_lo = m_lo / kBlk;
+  const int nmb = m_hi / kBlk - mb_lo + 1;
+  const int niter = nmb * p.group;
+
+  if (threadIdx.x == 0) {
+    init_barriers<HD>(bars, abort_flag);
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int krow = (int)(sq.k0 + n0);
+      mbar_expect_tx(&bars[L::bResFull], 2 * L::kTile);
+      for (int hf = 0; hf < L::kHalves; ++hf) {
+        tma_load_4d(smem + L::kResA + hf * 16384, &tm_k, &bars[L::bResFull], hf * 64, krow, hk, sq.bidx);
+        tma_load_4d(smem + L::kResB + hf * 16384, &tm_v, &bars[L::bResFull], hf * 64, krow, hk, sq.bidx);
+      }
+      int issued = 0;
+      for (int i = 0; i < niter; ++i) {
+        const int s = i & 1;
+        const uint32_t ph = (uint32_t)(i >> 1) & 1u;
+        const int h = hk * p.group + i / nmb;
+        const int mrow = (int)(sq.q0 + (int64_t)(mb_lo + i % nmb) * kBlk);
+        if (!mbar_wait(&bars[L::bRingEmpty + s], ph ^ 1u, abort_flag, status, 0x1100 + i)) break;
+        mbar_expect_tx(&bars[L::bRingFull + s], 2 * L::kTile);
+        for (int hf = 0; hf < L::kHalves; ++hf) {
+          tma_load_4d(smem + L::kRingA + s * L::kTile + hf * 16384, &tm_q, &bars[L::bRingFull + s], hf * 64, mrow, h,
+                      sq.bidx);
+          tma_load_4d(smem + L::kRingB + s * L::kTile + hf * 16384, &tm_do, &bars[L::bRingFull + s], hf * 64, mrow, h,
+                      sq.bidx);
+        }
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        mbar_wait_quiet(&bars[L::bResFull], 0);
+        for (int i = max(0, issued - 2); i < issued; ++i) mbar_wait_quiet(&bars[L::bRingFull + (i & 1)], (uint32_t)(i >> 1) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
+      constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
+      const uint32_t k_addr = smem_u32(smem + L::kResA), v_addr = smem_u32(smem + L::kResB);
+      const uint32_t q_ring = smem_u32(smem + L::kRingA), do_ring = smem_u32(smem + L::kRingB);
+      auto issue_s = [&](int i) {      // S^T = K Q_i^T
+        const uint32_t qa = q_ring + (uint32_t)(i & 1) * L::kTile;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          mma_ss(tmem_base + kColS, desc_kmajor(k_addr, kk), desc_kmajor(qa, kk), kIdescSS, kk > 0);
+        mma_commit(&bars[L::bSFull]);
+      };
+      auto issue_dp = [&](int i) {     // dP^T = V dO_i^T
+        const uint32_t da = do_ring + (uint32_t)(i & 1) * L::kTile;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          mma_ss(tmem_base + kColDP, desc_kmajor(v_addr, kk), desc_kmajor(da, kk), kIdescSS, kk > 0);
+        mma_commit(&bars[L::bDpFull]);
+      };
+      bool ok = mbar_wait(&bars[L::bResFull], 0, abort_flag, status, 0x1200) &&
+                mbar_wait(&bars[L::bRingFull + 0], 0, abort_flag, status, 0x1201);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        issue_dp(0);
+      }
+      for (int i = 0; ok && i < niter; ++i) {
+        const int s = i & 1;
+        const uint32_t par = (uint32_t)i & 1u;
+        if (!mbar_wait(&bars[L::bPFull], par, abort_flag, status, 0x1300 + i)) break;
+        tc_fence_after();
+        {   // dV += P^T dO_i
+          const uint32_t da = do_ring + (uint32_t)s * L::kTile;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts(tmem_base + kColAcc0, tmem_base + kColS + split_a_col(kk), desc_mnmajor(da, kk), kIdescTS,
+                   (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        if (i + 1 < niter) {
+          if (!mbar_wait(&bars[L::bRingFull + ((i + 1) & 1)], (uint32_t)((i + 1) >> 1) & 1u, abort_flag, status,
+                         0x1400 + i))
+            break;
+          tc_fence_after();
+          issue_s(i + 1);
+        }
+        if (!mbar_wait(&bars[L::bDsFull], par, abort_flag, status, 0x1500 + i)) break;
+        tc_fence_after();
+        {   // dK += dS^T Q_i
+          const uint32_t qa = q_ring + (uint32_t)s * L::kTile;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + split_a_col(kk), desc_mnmajor(qa, kk), kIdescTS,
+                   (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(&bars[L::bRingEmpty + s]);
+        if (i + 1 < niter) issue_dp(i + 1);
+      }
+      mma_commit(&bars[L::bAccDone]);
+    }
+    __syncwarp();
+  } else if (warp == 2) {
+    // logsumexp (in log2 units) and delta of the streamed query block
+    for (int i = 0; i < niter; ++i) {
+      const int s = i & 1;
+      if (!mbar_wait(&bars[L::bAuxEmpty + s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag, status, 0x1600 + i)) break;
+      const int h = hk * p.group + i / nmb;
+      const int mbase = (mb_lo + i % nmb) * kBlk;
+      const int64_t lrow = lse_offset(p, sq, h);
+      float* dst = aux + s * 256;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int c = lane * 4 + t, m = mbase + c;
+        const bool in = m < sq.sq;
+        dst[c] = in ? p.lse[lrow + m] * kLog2e : INFINITY;
+        dst[128 + c] = in ? p.delta[lrow + m] : 0.f;
+      }
+      mbar_arrive(&bars[L::bAuxFull + s]);
+    }
+  } else if (warp >= 4) {
+    const int quarter = warp & 3, ch = (warp - 4) >> 2;
+    const int r = quarter * 32 + lane;
+    const int n = n0 + r;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int cbase = 64 * ch;
+    int col_lo = 0, col_hi = sq.sq - 1;     // valid query rows for this key
+    if (p.causal) {
+      int64_t lo = (int64_t)n - sq.wr, hi = (int64_t)n + sq.wl;
+      if (lo > col_lo) col_lo = (int)(lo > 0x7fffffffLL ? 0x7fffffffLL : lo);
+      if (hi < col_hi) col_hi = (int)(hi < -1 ? -1 : hi);
+    }
+    if (n >= sq.sk) { col_lo = 1; col_hi = 0; }
+    bool ok = true;
+    for (int i = 0; i < niter; ++i) {
+      const int s = i & 1;
+      const uint32_t par = (uint32_t)i & 1u;
+      const int h = hk * p.group + i / nmb;
+      const int mbase = (mb_lo + i % nmb) * kBlk + cbase;    // first query row of this thread's columns
+      const float* lse2 = aux + s * 256 + cbase;
+      const float* dlt = lse2 + 128;
+      if (!mbar_wait(&bars[L::bAuxFull + s], (uint32_t)(i >> 1) & 1u, abort_flag, status, 0x1700 + i)) { ok = false; break; }
+      if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x1800 + i)) { ok = false; break; }
+      tc_fence_after();
+      float pr[64];
+      tmem_ld32f(tmem_base + lane_addr + kColS + cbase, &pr[0]);
+      tmem_ld32f(tmem_base + lane_addr + kColS + cbase + 32, &pr[32]);
+      tmem_wait_ld();
+      const bool need_mask = !(mbase >= col_lo && mbase + 63 <= col_hi);
+      const bool any_mask = __any_sync(0xffffffffu, need_mask);
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float t = pr[c] * p.qk_scale;
+        if (p.has_bias) {
+          const int m = mbase + c;
+          if (m < sq.sq && n < sq.sk)
+            t = fmaf(to_f32<T>(reinterpret_cast<const T*>(p.bias.ptr)[(int64_t)sq.bidx * p.bias.s[0] +
+                                                                      (int64_t)h * p.bias.s[1] +
+                                                                      (int64_t)m * p.bias.s[2] +
+                                                                      (int64_t)n * p.bias.s[3]]),
+                     kLog2e, t);
+        }
+        float e = exp2f(t - lse2[c]);
+        if (any_mask) {
+          const int m = mbase + c;
+          e = (m >= col_lo && m <= col_hi) ? e : 0.f;
+        }
+        pr[c] = e;
+      }
+      uint64_t keep = ~0ull;
+      if (p.dropout_on) {
+        const DropoutCtx dctx = dropout_ctx(p, z, h);
+        const int nn = min(n, p.max_sk - 1);
+        keep = 0ull;
+#pragma unroll
+        for (int c = 0; c < 64; ++c)
+          if (dropout_keep(dctx, min(mbase + c, p.max_sq - 1), nn)) keep |= (1ull << c);
+      }
+      {
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float a = pr[2 * c], b = pr[2 * c + 1];
+          if (p.dropout_on) {
+            a = ((keep >> (2 * c)) & 1ull) ? a * p.dropout_scale : 0.f;
+            b = ((keep >> (2 * c + 1)) & 1ull) ? b * p.dropout_scale : 0.f;
+          }
+          pk[c] = pack2<T>(a, b);
+        }
+        tmem_st32(tmem_base + lane_addr + kColS + cbase, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bars[L::bPFull]);
+
+      if (!mbar_wait(&bars[L::bDpFull], par, abort_flag, status, 0x1900 + i)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float dp[32];
+        tmem_ld32f(tmem_base + lane_addr + kColDP + cbase + 32 * half, dp);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const int c0 = 32 * half + 2 * c;
+          float a = dp[2 * c], b = dp[2 * c + 1];
+          if (p.dropout_on) {
+            a = ((keep >> c0) & 1ull) ? a * p.dropout_scale : 0.f;
+            b = ((keep >> (c0 + 1)) & 1ull) ? b * p.dropout_scale : 0.f;
+          }
+          pk[c] = pack2<T>(pr[c0] * (a - dlt[c0]), pr[c0 + 1] * (b - dlt[c0 + 1]));
+        }
+        tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16 * half, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bars[L::bDsFull]);
+      mbar_arrive(&bars[L::bAuxEmpty + s]);
+    }
+    if (ok) ok = mbar_wait(&bars[L::bAccDone], 0, abort_flag, status, 0x1A00);
+    if (ok) {
+      tc_fence_after();
+      constexpr int kCols = HD / 2;          // columns of dV / dK per warpgroup
+      T* dvp = reinterpret_cast<T*>(p.dv.ptr) + (int64_t)sq.bidx * p.dv.s[0] + (int64_t)hk * p.dv.s[1] +
+               (sq.k0 + n) * p.dv.s[2];
+      T* dkp = reinterpret_cast<T*>(p.dk.ptr) + (int64_t)sq.bidx * p.dk.s[0] + (int64_t)hk * p.dk.s[1] +
+               (sq.k0 + n) * p.dk.s[2];
+#pragma unroll
+      for (int c = 0; c < kCols / 32; ++c) {
+        float v[32];
+        const int d0 = ch * kCols + c * 32;
+        tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
+        tmem_wait_ld();
+        if (n < sq.sk) store_row_chunk32<T>(dvp, v, 1.0f, d0, p.dvo);
+        tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
+        tmem_wait_ld();
+        if (n < sq.sk) store_row_chunk32<T>(dkp, v, p.sm_scale, d0, p.dqk);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// =========================================================================================
+// dQ (+ dBias).  grid = (cdiv(max_sq, 128), Hq, batch)
+template <typename T, int HD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tm_q,
+                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                    const __grid_constant__ CUtensorMap tm_do, unsigned int* status) {
+  using L = BwdSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAbort);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int z = blockIdx.z, h = blockIdx.y;
+  const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * kBlk;
+  if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
+  const Seq sq = resolve_seq(p, z);
+  if (m0 >= sq.sq) return;
+  const int hk = h / p.group;
+  int n_lo, n_hi;
+  key_range(p, sq, m0, min(m0 + kBlk, sq.sq) - 1, n_lo, n_hi);
+  if (n_hi < n_lo) {
+    zero_rows<T>(p.dq, sq.bidx, h, sq.q0, m0, sq.sq, p.dqk);
+    return;
+  }
+  const int jb_lo = n_lo / kBlk;
+  const int niter = n_hi / kBlk - jb_lo + 1;
+
+  if (threadIdx.x == 0) {
+    init_barriers<HD>(bars, abort_flag);
+    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int qrow = (int)(sq.q0 + m0);
+      mbar_expect_tx(&bars[L::bResFull], 2 * L::kTile);
+      for (int hf = 0; hf < L::kHalves; ++hf) {
+        tma_load_4d(smem + L::kResA + hf * 16384, &tm_q, &bars[L::bResFull], hf * 64, qrow, h, sq.bidx);
+        tma_load_4d(smem + L::kResB + hf * 16384, &tm_do, &bars[L::bResFull], hf * 64, qrow, h, sq.bidx);
+      }
+      int issued = 0;
+      for (int i = 0; i < niter; ++i) {
+        const int s = i & 1;
+        const uint32_t ph = (uint32_t)(i >> 1) & 1u;
+        const int krow = (int)(sq.k0 + (int64_t)(jb_lo + i) * kBlk);
+        if (!mbar_wait(&bars[L::bRingEmpty + s], ph ^ 1u, abort_flag, status, 0x2100 + i)) break;
+        mbar_expect_tx(&bars[L::bRingFull + s], 2 * L::kTile);
+        for (int hf = 0; hf < L::kHalves; ++hf) {
+          tma_load_4d(smem + L::kRingA + s * L::kTile + hf * 16384, &tm_k, &bars[L::bRingFull + s], hf * 64, krow, hk,
+                      sq.bidx);
+          tma_load_4d(smem + L::kRingB + s * L::kTile + hf * 16384, &tm_v, &bars[L::bRingFull + s], hf * 64, krow, hk,
+                      sq.bidx);
+        }
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        mbar_wait_quiet(&bars[L::bResFull], 0);
+        for (int i = max(0, issued - 2); i < issued; ++i) mbar_wait_quiet(&bars[L::bRingFull + (i & 1)], (uint32_t)(i >> 1) & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
+      constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
+      const uint32_t q_addr = smem_u32(smem + L::kResA), do_addr = smem_u32(smem + L::kResB);
+      const uint32_t k_ring = smem_u32(smem + L::kRingA), v_ring = smem_u32(smem + L::kRingB);
+      auto issue_s = [&](int i) {      // S = Q K_i^T
+        const uint32_t ka = k_ring + (uint32_t)(i & 1) * L::kTile;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          mma_ss(tmem_base + kColS, desc_kmajor(q_addr, kk), desc_kmajor(ka, kk), kIdescSS, kk > 0);
+        mma_commit(&bars[L::bSFull]);
+      };
+      auto issue_dp = [&](int i) {     // dP = dO V_i^T
+        const uint32_t va = v_ring + (uint32_t)(i & 1) * L::kTile;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          mma_ss(tmem_base + kColDP, desc_kmajor(do_addr, kk), desc_kmajor(va, kk), kIdescSS, kk > 0);
+        mma_commit(&bars[L::bDpFull]);
+      };
+      bool ok = mbar_wait(&bars[L::bResFull], 0, abort_flag, status, 0x2200) &&
+                mbar_wait(&bars[L::bRingFull + 0], 0, abort_flag, status, 0x2201);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        issue_dp(0);
+      }
+      for (int i = 0; ok && i < niter; ++i) {
+        const int s = i & 1;
+        const uint32_t par = (uint32_t)i & 1u;
+        if (i + 1 < niter) {
+          // S_i has been copied to registers by every compute thread: its buffer is free.
+          if (!mbar_wait(&bars[L::bSRead], par, abort_flag, status, 0x2300 + i)) break;
+          if (!mbar_wait(&bars[L::bRingFull + ((i + 1) & 1)], (uint32_t)((i + 1) >> 1) & 1u, abort_flag, status,
+                         0x2400 + i))
+            break;
+          tc_fence_after();
+          issue_s(i + 1);
+        }
+        if (!mbar_wait(&bars[L::bDsFull], par, abort_flag, status, 0x2500 + i)) break;
+        tc_fence_after();
+        {   // dQ += dS K_i
+          const uint32_t ka = k_ring + (uint32_t)s * L::kTile;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts(tmem_base + kColAcc0, tmem_base + kColDP + split_a_col(kk), desc_mnmajor(ka, kk), kIdescTS,
+                   (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(&bars[L::bRingEmpty + s]);
+        if (i + 1 < niter) issue_dp(i + 1);
+      }
+      mma_commit(&bars[L::bAccDone]);
+    }
+    __syncwarp();
+  } else if (warp >= 4) {
+    const int quarter = warp & 3, ch = (warp - 4) >> 2;
+    const int r = quarter * 32 + lane;
+    const int m = m0 + r;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int cbase = 64 * ch;
+    int row_lo = 0, row_hi = sq.sk - 1;     // valid keys for this query row
+    if (p.causal) {
+      int64_t lo = (int64_t)m - sq.wl, hi = (int64_t)m + sq.wr;
+      if (lo > row_lo) row_lo = (int)(lo > 0x7fffffffLL ? 0x7fffffffLL : lo);
+      if (hi < row_hi) row_hi = (int)(hi < -1 ? -1 : hi);
+    }
+    if (m >= sq.sq) { row_lo = 1; row_hi = 0; }
+    const int64_t lrow = lse_offset(p, sq, h);
+    const float lse2 = (m < sq.sq) ? p.lse[lrow + m] * kLog2e : INFINITY;
+    const float dlt = (m < sq.sq) ? p.delta[lrow + m] : 0.f;
+    DropoutCtx dctx;
+    if (p.dropout_on) dctx = dropout_ctx(p, z, h);
+    const int mm = min(m, sq.sq - 1);
+    const T* bias_row = p.has_bias ? reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
+                                         (int64_t)h * p.bias.s[1] + (int64_t)mm * p.bias.s[2]
+                                   : nullptr;
+    T* db_row = p.has_dbias ? reinterpret_cast<T*>(p.dbias.ptr) + (int64_t)sq.bidx * p.dbias.s[0] +
+                                  (int64_t)h * p.dbias.s[1] + (int64_t)mm * p.dbias.s[2]
+                            : nullptr;
+    bool ok = true;
+    for (int i = 0; i < niter; ++i) {
+      const uint32_t par = (uint32_t)i & 1u;
+      const int nbase = (jb_lo + i) * kBlk + cbase;     // first key of this thread's columns
+      if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x2600 + i)) { ok = false; break; }
+      tc_fence_after();
+      float pr[64];
+      tmem_ld32f(tmem_base + lane_addr + kColS + cbase, &pr[0]);
+      tmem_ld32f(tmem_base + lane_addr + kColS + cbase + 32, &pr[32]);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&bars[L::bSRead]);
+      const bool need_mask = !(nbase >= row_lo && nbase + 63 <= row_hi);
+      const bool any_mask = __any_sync(0xffffffffu, need_mask);
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float t = pr[c] * p.qk_scale;
+        if (p.has_bias) {
+          const int n = nbase + c;
+          if (n < sq.sk) t = fmaf(to_f32<T>(bias_row[(int64_t)n * p.bias.s[3]]), kLog2e, t);
+        }
+        float e = exp2f(t - lse2);
+        if (any_mask) {
+          const int n = nbase + c;
+          e = (n >= row_lo && n <= row_hi) ? e : 0.f;
+        }
+        pr[c] = e;
+      }
+      uint64_t keep = ~0ull;
+      if (p.dropout_on) {
+        keep = 0ull;
+        const int md = min(m, p.max_sq - 1);
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4)
+          keep |= (uint64_t)dropout_keep4(dctx, md, (nbase >> 2) + c4) << (4 * c4);
+      }
+      if (!mbar_wait(&bars[L::bDpFull], par, abort_flag, status, 0x2700 + i)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float dp[32];
+        tmem_ld32f(tmem_base + lane_addr + kColDP + cbase + 32 * half, dp);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const int c0 = 32 * half + 2 * c;
+          float a = dp[2 * c], b = dp[2 * c + 1];
+          if (p.dropout_on) {
+            a = ((keep >> c0) & 1ull) ? a * p.dropout_scale : 0.f;
+            b = ((keep >> (c0 + 1)) & 1ull) ? b * p.dropout_scale : 0.f;
+          }
+          pk[c] = pack2<T>(pr[c0] * (a - dlt), pr[c0 + 1] * (b - dlt));
+        }
+        if (p.has_dbias && m < sq.sq) {
+          // dB = cast(dS): the packed pairs are exactly the values to store
+          const int nb = nbase + 32 * half;
+          if (p.dbias.s[3] == 1 && nb + 32 <= sq.sk &&
+              (reinterpret_cast<uintptr_t>(db_row + nb) & 15u) == 0) {
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4)
+              *reinterpret_cast<uint4*>(db_row + nb + v4 * 8) =
+                  make_uint4(pk[v4 * 4], pk[v4 * 4 + 1], pk[v4 * 4 + 2], pk[v4 * 4 + 3]);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int n = nb + c;
+              if (n < sq.sk) {
+                const uint16_t bits = (uint16_t)((pk[c >> 1] >> ((c & 1) * 16)) & 0xffffu);
+                reinterpret_cast<uint16_t*>(db_row)[(int64_t)n * p.dbias.s[3]] = bits;
+              }
+            }
+          }
+        }
+        tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16 * half, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bars[L::bDsFull]);
+    }
+    if (ok) ok = mbar_wait(&bars[L::bAccDone], 0, abort_flag, status, 0x2800);
+    if (ok) {
+      tc_fence_after();
+      constexpr int kCols = HD / 2;
+      T* dqp = reinterpret_cast<T*>(p.dq.ptr) + (int64_t)sq.bidx * p.dq.s[0] + (int64_t)h * p.dq.s[1] +
+               (sq.q0 + m) * p.dq.s[2];
+#pragma unroll
+      for (int c = 0; c < kCols / 32; ++c) {
+        float v[32];
+        const int d0 = ch * kCols + c * 32;
+        tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
+        tmem_wait_ld();
+        if (m < sq.sq) store_row_chunk32<T>(dqp, v, p.sm_scale, d0, p.dqk);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <typename T, int HD>
+cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st) {
+  using L = BwdSmem<HD>;
+  CUtensorMap tq, tk, tv, tdo;
+  if (!make_tile_map_16bit(&tq, p.q, p.dqk, p.q.n[2], kBlk) || !make_tile_map_16bit(&tk, p.k, p.dqk, p.k.n[2], kBlk) ||
+      !make_tile_map_16bit(&tv, p.v, p.dvo, p.v.n[2], kBlk) ||
+      !make_tile_map_16bit(&tdo, p.dout, p.dvo, p.dout.n[2], kBlk))
+    return cudaErrorInvalidValue;
+  unsigned int* status = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_sm100_bwd_status);
+  if (e != cudaSuccess) return e;
+  if (which == 1) {
+    e = cudaFuncSetAttribute(sm100_bwd_dkdv_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess) return e;
+    dim3 grid((p.max_sk + kBlk - 1) / kBlk, p.hk, p.batch);
+    sm100_bwd_dkdv_kernel<T, HD><<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status);
+  } else {
+    e = cudaFuncSetAttribute(sm100_bwd_dq_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess) return e;
+    dim3 grid((p.max_sq + kBlk - 1) / kBlk, p.hq, p.batch);
+    sm100_bwd_dq_kernel<T, HD><<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status);
+  }
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bwd(int which, int dtype, const Params& p, cudaStream_t st) {
+  const bool small = p.dqk <= 64 && p.dvo <= 64;
+  if (dtype == 2) return small ? launch_bwd_T<__half, 64>(which, p, st) : launch_bwd_T<__half, 128>(which, p, st);
+  return small ? launch_bwd_T<__nv_bfloat16, 64>(which, p, st) : launch_bwd_T<__nv_bfloat16, 128>(which, p, st);
+}
+
+}  // namespace
+
+bool sm100_bwd_supported(int dtype, const Params& p) {
+  if (dtype != 2 && dtype != 3) return false;
+  if (p.dqk > 128 || p.dvo > 128 || p.dqk % 8 != 0 || p.dvo % 8 != 0) return false;
+  if (p.max_sq <= 0 || p.max_sk <= 0 || p.batch <= 0) return false;
+  if (!tma_friendly(p.q) || !tma_friendly(p.k) || !tma_friendly(p.v) || !tma_friendly(p.dout)) return false;
+  if (p.q.n[3] != p.dqk || p.k.n[3] != p.dqk || p.v.n[3] != p.dvo || p.dout.n[3] != p.dvo) return false;
+  // gradients are written with 16-byte vector stores (absent ones are not written at all)
+  if (p.dq.ptr && !vector_store_friendly(p.dq)) return false;
+  if (p.dk.ptr && !vector_store_friendly(p.dk)) return false;
+  if (p.dv.ptr && !vector_store_friendly(p.dv)) return false;
+  return tensor_map_encoder() != nullptr;
+}
+
+cudaError_t launch_sm100_bwd_dkdv(int dtype, const Params& p, cudaStream_t st) { return launch_bwd(1, dtype, p, st); }
+cudaError_t launch_sm100_bwd_dq(int dtype, const Params& p, cudaStream_t st) { return launch_bwd(2, dtype, p, st); }
+
+unsigned int sm100_bwd_status(bool reset) {
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_sm100_bwd_status, sizeof(v)) != cudaSuccess) { (void)cudaGetLastError(); return 0xffffffffu; }
+  if (reset && v != 0) {
+    unsigned int zero = 0;
+    if (cudaMemcpyToSymbol(g_sm100_bwd_status, &zero, sizeof(zero)) != cudaSuccess) (void)cudaGetLastError();
+  }
+  return v;
+}
+
+}  // namespace ab200

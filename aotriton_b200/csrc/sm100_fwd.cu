@@ -31,7 +31,7 @@
 
 namespace ab200 {
 
-__device__ unsigned int g_sm100_status = 0;
+__device__ unsigned int g_sm100_fwd_status = 0;
 
 namespace {
 
@@ -58,23 +58,6 @@ struct FwdSmem {
   static constexpr int kTotal = kAbort + 4;
   static constexpr int kDynamic = kTotal + 1024;             // slack for manual 1024-byte alignment
 };
-
-template <typename T> struct Fmt;
-template <> struct Fmt<__half> { static constexpr uint32_t code = 0; };
-template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t code = 1; };
-
-template <typename T>
-__device__ __forceinline__ uint32_t pack2(float a, float b);
-template <>
-__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-template <>
-__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 // Rows of the tile that have no key at all: O = 0, LSE = +inf.
 template <typename T>
@@ -105,16 +88,16 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
   const int z = blockIdx.z, h = blockIdx.y;
   const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * kBM;     // long tiles of a causal problem first
   if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;   // an earlier CTA timed out
-  const Seq sq = resolve_seq(p, z);
-  if (m0 >= sq.sq) return;
-  const int hk = h / p.group;
-
+  // One thread of the grid reports the seed and offset actually used, before any early exit.
   if (p.dropout_on && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
     uint64_t seed = p.seed_ptr ? *p.seed_ptr : 0ull;
     uint64_t base = p.off2 + (p.off1_ptr ? *p.off1_ptr : 0ull);
     if (p.seed_out) *p.seed_out = seed;
     if (p.off_out) *p.off_out = base;
   }
+  const Seq sq = resolve_seq(p, z);
+  if (m0 >= sq.sq) return;
+  const int hk = h / p.group;
 
   int n_lo, n_hi;
   key_range(p, sq, m0, min(m0 + kBM, sq.sq) - 1, n_lo, n_hi);
@@ -381,17 +364,6 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
   }
 }
 
-bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
-
-bool tma_friendly(const View4& v) {
-  if (!aligned16(v.ptr)) return false;
-  for (int i = 0; i < 3; ++i)
-    if (v.n[i] > 1 && (v.s[i] % 8 != 0 || v.s[i] <= 0)) return false;
-  for (int i = 0; i < 4; ++i)
-    if (v.n[i] <= 0 || v.n[i] > 0x7fffffffLL) return false;
-  return v.s[3] == 1;
-}
-
 template <typename T, int HD>
 cudaError_t launch_fwd_T(const Params& p, cudaStream_t st) {
   using L = FwdSmem<HD>;
@@ -405,7 +377,7 @@ cudaError_t launch_fwd_T(const Params& p, cudaStream_t st) {
                                        L::kDynamic);
   if (e != cudaSuccess) return e;
   unsigned int* status = nullptr;
-  e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_sm100_status);
+  e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_sm100_fwd_status);
   if (e != cudaSuccess) return e;
   dim3 grid((p.max_sq + kBM - 1) / kBM, p.hq, p.batch);
   sm100_fwd_kernel<T, HD><<<grid, kFwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, status);
@@ -432,12 +404,12 @@ cudaError_t launch_sm100_fwd(int dtype, const Params& p, cudaStream_t st) {
   return small ? launch_fwd_T<__nv_bfloat16, 64>(p, st) : launch_fwd_T<__nv_bfloat16, 128>(p, st);
 }
 
-unsigned int sm100_read_status(bool reset) {
+unsigned int sm100_fwd_status(bool reset) {
   unsigned int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_sm100_status, sizeof(v)) != cudaSuccess) { (void)cudaGetLastError(); return 0xffffffffu; }
+  if (cudaMemcpyFromSymbol(&v, g_sm100_fwd_status, sizeof(v)) != cudaSuccess) { (void)cudaGetLastError(); return 0xffffffffu; }
   if (reset && v != 0) {
     unsigned int zero = 0;
-    if (cudaMemcpyToSymbol(g_sm100_status, &zero, sizeof(zero)) != cudaSuccess) (void)cudaGetLastError();
+    if (cudaMemcpyToSymbol(g_sm100_fwd_status, &zero, sizeof(zero)) != cudaSuccess) (void)cudaGetLastError();
   }
   return v;
 }

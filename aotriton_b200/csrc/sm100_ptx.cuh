@@ -6,7 +6,10 @@
 
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
 #include <stdint.h>
+#include "common.cuh"
 
 namespace ab200 {
 namespace ptx {
@@ -215,6 +218,41 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 }  // namespace ptx
+
+// ---- element-type helpers shared by the tcgen05 kernels ------------------------------
+template <typename T> struct Fmt;
+template <> struct Fmt<__half> { static constexpr uint32_t code = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t code = 1; };
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
+
+// A view the TMA tile maps can describe: 16-byte aligned base and outer strides, unit inner stride.
+inline bool tma_friendly(const View4& v) {
+  if (v.ptr == nullptr || !aligned16(v.ptr)) return false;
+  for (int i = 0; i < 3; ++i)
+    if (v.n[i] > 1 && (v.s[i] % 8 != 0 || v.s[i] <= 0)) return false;
+  for (int i = 0; i < 4; ++i)
+    if (v.n[i] <= 0 || v.n[i] > 0x7fffffffLL) return false;
+  return v.s[3] == 1;
+}
+
+// Rows written with 16-byte vector stores.
+inline bool vector_store_friendly(const View4& v) {
+  return v.ptr != nullptr && aligned16(v.ptr) && v.s[0] % 8 == 0 && v.s[1] % 8 == 0 && v.s[2] % 8 == 0 && v.s[3] == 1;
+}
 
 // ---- host side: TMA descriptor encoding without linking libcuda ----------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
