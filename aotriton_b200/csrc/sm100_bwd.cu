@@ -304,24 +304,33 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       tmem_wait_ld();
       const bool need_mask = !(mbase >= col_lo && mbase + 63 <= col_hi);
       const bool any_mask = __any_sync(0xffffffffu, need_mask);
+      // exponent arguments: scaled score (+ bias) minus the row's logsumexp, all in log2 units.
+      // Scale first, subtract second, so that the forward's reference point cancels exactly.
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float t = pr[c] * p.qk_scale;
-        if (p.has_bias) {
+      for (int c = 0; c < 64; ++c) pr[c] *= p.qk_scale;
+      if (p.has_bias && n < sq.sk) {
+        const T* bcol = reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
+                        (int64_t)h * p.bias.s[1] + (int64_t)n * p.bias.s[3];
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
           const int m = mbase + c;
-          if (m < sq.sq && n < sq.sk)
-            t = fmaf(to_f32<T>(reinterpret_cast<const T*>(p.bias.ptr)[(int64_t)sq.bidx * p.bias.s[0] +
-                                                                      (int64_t)h * p.bias.s[1] +
-                                                                      (int64_t)m * p.bias.s[2] +
-                                                                      (int64_t)n * p.bias.s[3]]),
-                     kLog2e, t);
+          if (m < sq.sq) pr[c] = fmaf(to_f32<T>(bcol[(int64_t)m * p.bias.s[2]]), kLog2e, pr[c]);
         }
-        float e = exp2f(t - lse2[c]);
-        if (any_mask) {
+      }
+#pragma unroll
+      for (int c4 = 0; c4 < 16; ++c4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
+        pr[4 * c4 + 0] = ex2(pr[4 * c4 + 0] - l4.x);
+        pr[4 * c4 + 1] = ex2(pr[4 * c4 + 1] - l4.y);
+        pr[4 * c4 + 2] = ex2(pr[4 * c4 + 2] - l4.z);
+        pr[4 * c4 + 3] = ex2(pr[4 * c4 + 3] - l4.w);
+      }
+      if (any_mask) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
           const int m = mbase + c;
-          e = (m >= col_lo && m <= col_hi) ? e : 0.f;
+          pr[c] = (m >= col_lo && m <= col_hi) ? pr[c] : 0.f;
         }
-        pr[c] = e;
       }
       uint64_t keep = ~0ull;
       if (p.dropout_on) {
@@ -356,16 +365,17 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         float dp[32];
         tmem_ld32f(tmem_base + lane_addr + kColDP + cbase + 32 * half, dp);
         tmem_wait_ld();
+        if (p.dropout_on) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) dp[c] = ((keep >> (32 * half + c)) & 1ull) ? dp[c] * p.dropout_scale : 0.f;
+        }
         uint32_t pk[16];
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const int c0 = 32 * half + 2 * c;
-          float a = dp[2 * c], b = dp[2 * c + 1];
-          if (p.dropout_on) {
-            a = ((keep >> c0) & 1ull) ? a * p.dropout_scale : 0.f;
-            b = ((keep >> (c0 + 1)) & 1ull) ? b * p.dropout_scale : 0.f;
-          }
-          pk[c] = pack2<T>(pr[c0] * (a - dlt[c0]), pr[c0 + 1] * (b - dlt[c0 + 1]));
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const int c0 = 32 * half + 4 * c4;
+          const float4 d4 = *reinterpret_cast<const float4*>(dlt + c0);
+          pk[2 * c4] = pack2<T>(pr[c0] * (dp[4 * c4] - d4.x), pr[c0 + 1] * (dp[4 * c4 + 1] - d4.y));
+          pk[2 * c4 + 1] = pack2<T>(pr[c0 + 2] * (dp[4 * c4 + 2] - d4.z), pr[c0 + 3] * (dp[4 * c4 + 3] - d4.w));
         }
         tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16 * half, pk);
       }
@@ -570,18 +580,22 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       const bool need_mask = !(nbase >= row_lo && nbase + 63 <= row_hi);
       const bool any_mask = __any_sync(0xffffffffu, need_mask);
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float t = pr[c] * p.qk_scale;
-        if (p.has_bias) {
+      for (int c = 0; c < 64; ++c) pr[c] *= p.qk_scale;
+      if (p.has_bias) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
           const int n = nbase + c;
-          if (n < sq.sk) t = fmaf(to_f32<T>(bias_row[(int64_t)n * p.bias.s[3]]), kLog2e, t);
+          if (n < sq.sk) pr[c] = fmaf(to_f32<T>(bias_row[(int64_t)n * p.bias.s[3]]), kLog2e, pr[c]);
         }
-        float e = exp2f(t - lse2);
-        if (any_mask) {
+      }
+#pragma unroll
+      for (int c = 0; c < 64; ++c) pr[c] = ex2(pr[c] - lse2);
+      if (any_mask) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
           const int n = nbase + c;
-          e = (n >= row_lo && n <= row_hi) ? e : 0.f;
+          pr[c] = (n >= row_lo && n <= row_hi) ? pr[c] : 0.f;
         }
-        pr[c] = e;
       }
       uint64_t keep = ~0ull;
       if (p.dropout_on) {

@@ -251,30 +251,60 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32f(s_addr + c * 32, &sc[c * 32]);
       tmem_wait_ld();
-#pragma unroll
-      for (int c = 0; c < 128; ++c) sc[c] *= p.qk_scale;
-      if (p.has_bias) {
-        const int nmax = sq.sk - n0;
-#pragma unroll
-        for (int c = 0; c < 128; ++c)
-          if (c < nmax) sc[c] = fmaf(to_f32<T>(bias_row[(int64_t)(n0 + c) * p.bias.s[3]]), kLog2e, sc[c]);
-      }
+      // Scores -> exponent arguments.  The common case (no bias, positive scale, ordinary
+      // magnitudes) keeps the raw scores and folds scale and maximum into one FMA per element
+      // later.  Otherwise the scaled scores are formed first, so that equal raw scores give
+      // exactly equal arguments however large they are.
       const bool need_mask = !(n0 >= row_lo && n0 + kBN - 1 <= row_hi);
-      if (__any_sync(0xffffffffu, need_mask)) {
+      const bool any_mask = __any_sync(0xffffffffu, need_mask);
+      bool simple = !p.has_bias && p.qk_scale > 0.f;
+      float mx;
+      if (simple) {
+        if (any_mask) {
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          const int n = n0 + c;
-          sc[c] = (n >= row_lo && n <= row_hi) ? sc[c] : -INFINITY;
+          for (int c = 0; c < 128; ++c) {
+            const int n = n0 + c;
+            sc[c] = (n >= row_lo && n <= row_hi) ? sc[c] : -INFINITY;
+          }
         }
-      }
-      float mx = sc[0];
+        float m8[8];
 #pragma unroll
-      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, sc[c]);
+        for (int c = 0; c < 8; ++c) m8[c] = sc[c];
+#pragma unroll
+        for (int c = 8; c < 128; ++c) m8[c & 7] = fmaxf(m8[c & 7], sc[c]);
+        mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+        mx *= p.qk_scale;
+        const bool huge = fabsf(mx) > 1.0e6f && mx != -INFINITY;
+        if (__any_sync(0xffffffffu, huge)) simple = false;
+      }
+      if (!simple) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) sc[c] *= p.qk_scale;
+        if (p.has_bias) {
+          const int nmax = sq.sk - n0;
+#pragma unroll
+          for (int c = 0; c < 128; ++c)
+            if (c < nmax) sc[c] = fmaf(to_f32<T>(bias_row[(int64_t)(n0 + c) * p.bias.s[3]]), kLog2e, sc[c]);
+        }
+        if (any_mask) {
+#pragma unroll
+          for (int c = 0; c < 128; ++c) {
+            const int n = n0 + c;
+            sc[c] = (n >= row_lo && n <= row_hi) ? sc[c] : -INFINITY;
+          }
+        }
+        float m8[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) m8[c] = sc[c];
+#pragma unroll
+        for (int c = 8; c < 128; ++c) m8[c & 7] = fmaxf(m8[c & 7], sc[c]);
+        mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+      }
       // Advance the reference maximum only when it moved by more than the threshold.
       const bool grow = mx > m_used + kRescaleThreshold;     // false when mx == -inf
       float alpha = 1.f;
       if (grow) {
-        alpha = exp2f(m_used - mx);                          // m_used == -inf -> 0
+        alpha = ex2(m_used - mx);                            // m_used == -inf -> 0
         m_used = mx;
       }
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
@@ -294,12 +324,24 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       }
       l *= alpha;
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum = 0.f;
+      float s8[8];
 #pragma unroll
-      for (int c = 0; c < 128; ++c) {
-        sc[c] = exp2f(sc[c] - m_safe);
-        sum += sc[c];
+      for (int c = 0; c < 8; ++c) s8[c] = 0.f;
+      if (simple) {
+        const float neg_m = -m_safe;
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          sc[c] = ex2(fmaf(sc[c], p.qk_scale, neg_m));
+          s8[c & 7] += sc[c];
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          sc[c] = ex2(sc[c] - m_safe);
+          s8[c & 7] += sc[c];
+        }
       }
+      const float sum = ((s8[0] + s8[1]) + (s8[2] + s8[3])) + ((s8[4] + s8[5]) + (s8[6] + s8[7]));
       l += sum;
       if (p.dropout_on) {
         const int mm = min(m, p.max_sq - 1);

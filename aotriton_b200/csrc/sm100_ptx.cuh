@@ -41,28 +41,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait in the kernels is bounded by wall-clock time: after kWaitLimitNs without success the
-// waiter records where it gave up (in *status, a global word the host can read), raises the
-// CTA-wide abort flag and returns false.  All roles test the abort flag while they poll, so a
-// stuck pipeline drains within about one limit and the CTA exits normally; CTAs that start after
-// a failure was recorded return at once (the kernels test *status first).
-constexpr uint64_t kWaitLimitNs = 1000000000ull;   // 1 s
-
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
+// Every wait in the kernels is bounded: after kWaitLimitCycles SM cycles (about a second)
+// without success the waiter records where it gave up (in *status, a global word the host can
+// read), raises the CTA-wide abort flag and returns false.  All roles test the abort flag while
+// they poll, so a stuck pipeline drains within about one limit and the CTA exits normally; CTAs
+// that start after a failure was recorded return at once (the kernels test *status first).
+constexpr long long kWaitLimitCycles = 2000000000ll;
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           unsigned int* status, uint32_t where) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  const long long t0 = clock64();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 0u) {
+    if ((i & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) break;
+      if (clock64() - t0 > kWaitLimitCycles) break;
     }
   }
   *abort_flag = 1u;
@@ -72,9 +66,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 
 // Bounded wait without side effects, for draining copies on the failure path.
 __device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity) {
-  const uint64_t t0 = global_timer_ns();
+  const long long t0 = clock64();
   for (uint32_t i = 1; !mbar_try_wait(bar, parity); ++i)
-    if ((i & 63u) == 0u && global_timer_ns() - t0 > kWaitLimitNs) return;
+    if ((i & 255u) == 0u && clock64() - t0 > kWaitLimitCycles) return;
+}
+
+// 2^x on the special-function unit (flushes denormals; -inf -> 0).
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 // ---- proxies / fences -------------------------------------------------------------
