@@ -60,7 +60,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -143,10 +143,12 @@ def run_reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=WORK["B"],
+                    help="per-GPU batch; smaller values give a short run for profiler captures")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -166,7 +168,7 @@ def main():
     from aotriton_b200 import cabi, flash
     from aotriton_b200.flash import hipError_t
 
-    B, H, S, D = WORK["B"], WORK["H"], WORK["S"], WORK["D"]
+    B, H, S, D = args.batch, WORK["H"], WORK["S"], WORK["D"]
     warm = max(args.warmup, 3)
     dev = torch.device("cuda", local)
     g = torch.Generator().manual_seed(1234 + rank)
