@@ -3,15 +3,15 @@
 //
 // Both kernels recompute the probabilities from Q, K and the forward's logsumexp and share
 // one scheme.  A CTA owns 128 rows of its output (keys for dK/dV, queries for dQ) and walks
-// 128-wide blocks of the other sequence dimension.  Twelve warps:
+// 128-wide blocks of the other sequence dimension.  Twenty warps:
 //
 //   warp 0      TMA producer   resident operand pair once, then the streamed pair through a
 //                              2-stage ring (cp.async.bulk.tensor, 128-byte swizzle)
 //   warp 1      MMA issuer     one thread issues all tcgen05.mma and tcgen05.commit
 //   warp 2      (dK/dV only)   stages logsumexp*log2(e) and delta of the streamed query
 //                              block in shared memory
-//   warps 4-11  compute        thread = one output row of the 128x128 score tile (TMEM lane),
-//                              the two warpgroups split its columns 0-63 / 64-127
+//   warps 4-19  compute        thread = one output row of the 128x128 score tile (TMEM lane),
+//                              the four warpgroups split its columns 32 apiece
 //
 //   dK/dV, per query block i:   S^T = K Q_i^T      dP^T = V dO_i^T        (operands in smem)
 //                               P^T, dS^T computed in registers, written back over S^T / dP^T
@@ -22,8 +22,8 @@
 //
 // Tensor memory: [0,128) S / P, [128,256) dP / dS, [256,384) dV or dQ, [384,512) dK.
 // A warpgroup writes its packed 16-bit results into the first half of ITS OWN column range
-// (columns it has already read), so the two warpgroups never overwrite each other's input;
-// the MMA issuer addresses the two halves separately.
+// (columns it has already read), so the warpgroups never overwrite each other's input;
+// the MMA issuer addresses the four pieces separately.
 //
 // Arithmetic contract (ROCm/aotriton modules/flash/kernel/bwd_inner_dk_dv.py:117-256,
 // bwd_inner_dq.py:117-205, bwd_kernel_dk_dv.py:387-391, bwd_kernel_dq.py:374-376):
@@ -45,7 +45,9 @@ namespace {
 using namespace ptx;
 
 constexpr int kBlk = 128;
-constexpr int kBwdThreads = 384;
+constexpr int kBwdThreads = 640;
+constexpr int kComputeThreads = 512;   // warps 4..19
+constexpr int kWgCols = 32;            // score columns per compute warpgroup
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 384;
 
@@ -72,9 +74,9 @@ __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int kk) {
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int kk) {
   return smem_desc_sw128(tile_addr + (uint32_t)kk * 2048u, 16384, 1024);
 }
-// Column of the packed 16-bit A operand for k-step kk when two warpgroups each packed their
-// 64 source columns into the first 32 columns of their own half.
-__device__ __forceinline__ uint32_t split_a_col(int kk) { return (uint32_t)((kk < 4) ? kk * 8 : 64 + (kk - 4) * 8); }
+// Column of the packed 16-bit A operand for k-step kk (16 source columns = 8 packed columns):
+// each warpgroup packed its 32 source columns into the first 16 columns of its own range.
+__device__ __forceinline__ uint32_t split_a_col(int kk) { return (uint32_t)(kWgCols * (kk >> 1) + (kk & 1) * 8); }
 
 template <typename T>
 __device__ __forceinline__ void store_row_chunk32(T* dst, const float* v, float scale, int d0, int dmax) {
@@ -110,14 +112,14 @@ __device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t*
     mbar_init(&bars[L::bRingFull + s], 1);
     mbar_init(&bars[L::bRingEmpty + s], 1);
     mbar_init(&bars[L::bAuxFull + s], 32);
-    mbar_init(&bars[L::bAuxEmpty + s], 256);
+    mbar_init(&bars[L::bAuxEmpty + s], kComputeThreads);
   }
   mbar_init(&bars[L::bSFull], 1);
   mbar_init(&bars[L::bDpFull], 1);
-  mbar_init(&bars[L::bPFull], 256);
-  mbar_init(&bars[L::bDsFull], 256);
+  mbar_init(&bars[L::bPFull], kComputeThreads);
+  mbar_init(&bars[L::bDsFull], kComputeThreads);
   mbar_init(&bars[L::bAccDone], 1);
-  mbar_init(&bars[L::bSRead], 256);
+  mbar_init(&bars[L::bSRead], kComputeThreads);
   fence_barrier_init();
 }
 
@@ -275,11 +277,11 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       mbar_arrive(&bars[L::bAuxFull + s]);
     }
   } else if (warp >= 4) {
-    const int quarter = warp & 3, ch = (warp - 4) >> 2;
+    const int quarter = warp & 3, wg = (warp - 4) >> 2;
     const int r = quarter * 32 + lane;
     const int n = n0 + r;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const int cbase = 64 * ch;
+    const int cbase = kWgCols * wg;
     int col_lo = 0, col_hi = sq.sq - 1;     // valid query rows for this key
     if (p.causal) {
       int64_t lo = (int64_t)n - sq.wr, hi = (int64_t)n + sq.wl;
@@ -298,27 +300,26 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       if (!mbar_wait(&bars[L::bAuxFull + s], (uint32_t)(i >> 1) & 1u, abort_flag, status, 0x1700 + i)) { ok = false; break; }
       if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x1800 + i)) { ok = false; break; }
       tc_fence_after();
-      float pr[64];
-      tmem_ld32f(tmem_base + lane_addr + kColS + cbase, &pr[0]);
-      tmem_ld32f(tmem_base + lane_addr + kColS + cbase + 32, &pr[32]);
+      float pr[32];
+      tmem_ld32f(tmem_base + lane_addr + kColS + cbase, pr);
       tmem_wait_ld();
-      const bool need_mask = !(mbase >= col_lo && mbase + 63 <= col_hi);
+      const bool need_mask = !(mbase >= col_lo && mbase + kWgCols - 1 <= col_hi);
       const bool any_mask = __any_sync(0xffffffffu, need_mask);
       // exponent arguments: scaled score (+ bias) minus the row's logsumexp, all in log2 units.
       // Scale first, subtract second, so that the forward's reference point cancels exactly.
 #pragma unroll
-      for (int c = 0; c < 64; ++c) pr[c] *= p.qk_scale;
+      for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
       if (p.has_bias && n < sq.sk) {
         const T* bcol = reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
                         (int64_t)h * p.bias.s[1] + (int64_t)n * p.bias.s[3];
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int c = 0; c < 32; ++c) {
           const int m = mbase + c;
           if (m < sq.sq) pr[c] = fmaf(to_f32<T>(bcol[(int64_t)m * p.bias.s[2]]), kLog2e, pr[c]);
         }
       }
 #pragma unroll
-      for (int c4 = 0; c4 < 16; ++c4) {
+      for (int c4 = 0; c4 < 8; ++c4) {
         const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
         pr[4 * c4 + 0] = ex2(pr[4 * c4 + 0] - l4.x);
         pr[4 * c4 + 1] = ex2(pr[4 * c4 + 1] - l4.y);
@@ -327,32 +328,32 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       }
       if (any_mask) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int c = 0; c < 32; ++c) {
           const int m = mbase + c;
           pr[c] = (m >= col_lo && m <= col_hi) ? pr[c] : 0.f;
         }
       }
-      uint64_t keep = ~0ull;
+      uint32_t keep = 0xffffffffu;
       if (p.dropout_on) {
         const DropoutCtx dctx = dropout_ctx(p, z, h);
         const int nn = min(n, p.max_sk - 1);
-        keep = 0ull;
+        keep = 0u;
 #pragma unroll
-        for (int c = 0; c < 64; ++c)
-          if (dropout_keep(dctx, min(mbase + c, p.max_sq - 1), nn)) keep |= (1ull << c);
+        for (int c = 0; c < 32; ++c)
+          if (dropout_keep(dctx, min(mbase + c, p.max_sq - 1), nn)) keep |= (1u << c);
       }
       {
-        uint32_t pk[32];
+        uint32_t pk[16];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
+        for (int c = 0; c < 16; ++c) {
           float a = pr[2 * c], b = pr[2 * c + 1];
           if (p.dropout_on) {
-            a = ((keep >> (2 * c)) & 1ull) ? a * p.dropout_scale : 0.f;
-            b = ((keep >> (2 * c + 1)) & 1ull) ? b * p.dropout_scale : 0.f;
+            a = ((keep >> (2 * c)) & 1u) ? a * p.dropout_scale : 0.f;
+            b = ((keep >> (2 * c + 1)) & 1u) ? b * p.dropout_scale : 0.f;
           }
           pk[c] = pack2<T>(a, b);
         }
-        tmem_st32(tmem_base + lane_addr + kColS + cbase, pk);
+        tmem_st16(tmem_base + lane_addr + kColS + cbase, pk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -360,24 +361,22 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
 
       if (!mbar_wait(&bars[L::bDpFull], par, abort_flag, status, 0x1900 + i)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         float dp[32];
-        tmem_ld32f(tmem_base + lane_addr + kColDP + cbase + 32 * half, dp);
+        tmem_ld32f(tmem_base + lane_addr + kColDP + cbase, dp);
         tmem_wait_ld();
         if (p.dropout_on) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) dp[c] = ((keep >> (32 * half + c)) & 1ull) ? dp[c] * p.dropout_scale : 0.f;
+          for (int c = 0; c < 32; ++c) dp[c] = ((keep >> c) & 1u) ? dp[c] * p.dropout_scale : 0.f;
         }
         uint32_t pk[16];
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
-          const int c0 = 32 * half + 4 * c4;
-          const float4 d4 = *reinterpret_cast<const float4*>(dlt + c0);
-          pk[2 * c4] = pack2<T>(pr[c0] * (dp[4 * c4] - d4.x), pr[c0 + 1] * (dp[4 * c4 + 1] - d4.y));
-          pk[2 * c4 + 1] = pack2<T>(pr[c0 + 2] * (dp[4 * c4 + 2] - d4.z), pr[c0 + 3] * (dp[4 * c4 + 3] - d4.w));
+          const float4 d4 = *reinterpret_cast<const float4*>(dlt + 4 * c4);
+          pk[2 * c4] = pack2<T>(pr[4 * c4] * (dp[4 * c4] - d4.x), pr[4 * c4 + 1] * (dp[4 * c4 + 1] - d4.y));
+          pk[2 * c4 + 1] = pack2<T>(pr[4 * c4 + 2] * (dp[4 * c4 + 2] - d4.z), pr[4 * c4 + 3] * (dp[4 * c4 + 3] - d4.w));
         }
-        tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16 * half, pk);
+        tmem_st16(tmem_base + lane_addr + kColDP + cbase, pk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -385,24 +384,20 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       mbar_arrive(&bars[L::bAuxEmpty + s]);
     }
     if (ok) ok = mbar_wait(&bars[L::bAccDone], 0, abort_flag, status, 0x1A00);
-    if (ok) {
+    if (ok && wg < HD / 32) {
       tc_fence_after();
-      constexpr int kCols = HD / 2;          // columns of dV / dK per warpgroup
       T* dvp = reinterpret_cast<T*>(p.dv.ptr) + (int64_t)sq.bidx * p.dv.s[0] + (int64_t)hk * p.dv.s[1] +
                (sq.k0 + n) * p.dv.s[2];
       T* dkp = reinterpret_cast<T*>(p.dk.ptr) + (int64_t)sq.bidx * p.dk.s[0] + (int64_t)hk * p.dk.s[1] +
                (sq.k0 + n) * p.dk.s[2];
-#pragma unroll
-      for (int c = 0; c < kCols / 32; ++c) {
-        float v[32];
-        const int d0 = ch * kCols + c * 32;
-        tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
-        tmem_wait_ld();
-        if (n < sq.sk) store_row_chunk32<T>(dvp, v, 1.0f, d0, p.dvo);
-        tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
-        tmem_wait_ld();
-        if (n < sq.sk) store_row_chunk32<T>(dkp, v, p.sm_scale, d0, p.dqk);
-      }
+      float v[32];
+      const int d0 = wg * 32;
+      tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
+      tmem_wait_ld();
+      if (n < sq.sk) store_row_chunk32<T>(dvp, v, 1.0f, d0, p.dvo);
+      tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
+      tmem_wait_ld();
+      if (n < sq.sk) store_row_chunk32<T>(dkp, v, p.sm_scale, d0, p.dqk);
     }
   }
 
@@ -541,11 +536,11 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     }
     __syncwarp();
   } else if (warp >= 4) {
-    const int quarter = warp & 3, ch = (warp - 4) >> 2;
+    const int quarter = warp & 3, wg = (warp - 4) >> 2;
     const int r = quarter * 32 + lane;
     const int m = m0 + r;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const int cbase = 64 * ch;
+    const int cbase = kWgCols * wg;
     int row_lo = 0, row_hi = sq.sk - 1;     // valid keys for this query row
     if (p.causal) {
       int64_t lo = (int64_t)m - sq.wl, hi = (int64_t)m + sq.wr;
@@ -571,71 +566,63 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       const int nbase = (jb_lo + i) * kBlk + cbase;     // first key of this thread's columns
       if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x2600 + i)) { ok = false; break; }
       tc_fence_after();
-      float pr[64];
-      tmem_ld32f(tmem_base + lane_addr + kColS + cbase, &pr[0]);
-      tmem_ld32f(tmem_base + lane_addr + kColS + cbase + 32, &pr[32]);
+      float pr[32];
+      tmem_ld32f(tmem_base + lane_addr + kColS + cbase, pr);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&bars[L::bSRead]);
-      const bool need_mask = !(nbase >= row_lo && nbase + 63 <= row_hi);
+      const bool need_mask = !(nbase >= row_lo && nbase + kWgCols - 1 <= row_hi);
       const bool any_mask = __any_sync(0xffffffffu, need_mask);
 #pragma unroll
-      for (int c = 0; c < 64; ++c) pr[c] *= p.qk_scale;
+      for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
       if (p.has_bias) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int c = 0; c < 32; ++c) {
           const int n = nbase + c;
           if (n < sq.sk) pr[c] = fmaf(to_f32<T>(bias_row[(int64_t)n * p.bias.s[3]]), kLog2e, pr[c]);
         }
       }
 #pragma unroll
-      for (int c = 0; c < 64; ++c) pr[c] = ex2(pr[c] - lse2);
+      for (int c = 0; c < 32; ++c) pr[c] = ex2(pr[c] - lse2);
       if (any_mask) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int c = 0; c < 32; ++c) {
           const int n = nbase + c;
           pr[c] = (n >= row_lo && n <= row_hi) ? pr[c] : 0.f;
         }
       }
-      uint64_t keep = ~0ull;
+      uint32_t keep = 0xffffffffu;
       if (p.dropout_on) {
-        keep = 0ull;
+        keep = 0u;
         const int md = min(m, p.max_sq - 1);
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4)
-          keep |= (uint64_t)dropout_keep4(dctx, md, (nbase >> 2) + c4) << (4 * c4);
+        for (int c4 = 0; c4 < 8; ++c4) keep |= dropout_keep4(dctx, md, (nbase >> 2) + c4) << (4 * c4);
       }
       if (!mbar_wait(&bars[L::bDpFull], par, abort_flag, status, 0x2700 + i)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         float dp[32];
-        tmem_ld32f(tmem_base + lane_addr + kColDP + cbase + 32 * half, dp);
+        tmem_ld32f(tmem_base + lane_addr + kColDP + cbase, dp);
         tmem_wait_ld();
+        if (p.dropout_on) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) dp[c] = ((keep >> c) & 1u) ? dp[c] * p.dropout_scale : 0.f;
+        }
         uint32_t pk[16];
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const int c0 = 32 * half + 2 * c;
-          float a = dp[2 * c], b = dp[2 * c + 1];
-          if (p.dropout_on) {
-            a = ((keep >> c0) & 1ull) ? a * p.dropout_scale : 0.f;
-            b = ((keep >> (c0 + 1)) & 1ull) ? b * p.dropout_scale : 0.f;
-          }
-          pk[c] = pack2<T>(pr[c0] * (a - dlt), pr[c0 + 1] * (b - dlt));
-        }
+        for (int c = 0; c < 16; ++c)
+          pk[c] = pack2<T>(pr[2 * c] * (dp[2 * c] - dlt), pr[2 * c + 1] * (dp[2 * c + 1] - dlt));
         if (p.has_dbias && m < sq.sq) {
           // dB = cast(dS): the packed pairs are exactly the values to store
-          const int nb = nbase + 32 * half;
-          if (p.dbias.s[3] == 1 && nb + 32 <= sq.sk &&
-              (reinterpret_cast<uintptr_t>(db_row + nb) & 15u) == 0) {
+          if (p.dbias.s[3] == 1 && nbase + 32 <= sq.sk && (reinterpret_cast<uintptr_t>(db_row + nbase) & 15u) == 0) {
 #pragma unroll
             for (int v4 = 0; v4 < 4; ++v4)
-              *reinterpret_cast<uint4*>(db_row + nb + v4 * 8) =
+              *reinterpret_cast<uint4*>(db_row + nbase + v4 * 8) =
                   make_uint4(pk[v4 * 4], pk[v4 * 4 + 1], pk[v4 * 4 + 2], pk[v4 * 4 + 3]);
           } else {
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
-              const int n = nb + c;
+              const int n = nbase + c;
               if (n < sq.sk) {
                 const uint16_t bits = (uint16_t)((pk[c >> 1] >> ((c & 1) * 16)) & 0xffffu);
                 reinterpret_cast<uint16_t*>(db_row)[(int64_t)n * p.dbias.s[3]] = bits;
@@ -643,26 +630,22 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
             }
           }
         }
-        tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16 * half, pk);
+        tmem_st16(tmem_base + lane_addr + kColDP + cbase, pk);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&bars[L::bDsFull]);
     }
     if (ok) ok = mbar_wait(&bars[L::bAccDone], 0, abort_flag, status, 0x2800);
-    if (ok) {
+    if (ok && wg < HD / 32) {
       tc_fence_after();
-      constexpr int kCols = HD / 2;
       T* dqp = reinterpret_cast<T*>(p.dq.ptr) + (int64_t)sq.bidx * p.dq.s[0] + (int64_t)h * p.dq.s[1] +
                (sq.q0 + m) * p.dq.s[2];
-#pragma unroll
-      for (int c = 0; c < kCols / 32; ++c) {
-        float v[32];
-        const int d0 = ch * kCols + c * 32;
-        tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
-        tmem_wait_ld();
-        if (m < sq.sq) store_row_chunk32<T>(dqp, v, p.sm_scale, d0, p.dqk);
-      }
+      float v[32];
+      const int d0 = wg * 32;
+      tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
+      tmem_wait_ld();
+      if (m < sq.sq) store_row_chunk32<T>(dqp, v, p.sm_scale, d0, p.dqk);
     }
   }
 

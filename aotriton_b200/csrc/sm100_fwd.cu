@@ -366,6 +366,10 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       mbar_arrive(&bars[L::bPFull + sb]);
     }
     // ---- epilogue ---------------------------------------------------------------------
+    // Holding S of the last block only guarantees that P V of all blocks but the last two has
+    // completed, and a parity wait can tell apart just two consecutive phases: wait for the
+    // last-but-one phase first, then for the last.
+    if (ok && nblk >= 2) ok = mbar_wait(&bars[L::bPvDone], (uint32_t)(nblk - 2) & 1u, abort_flag, status, 0x8FF);
     if (ok) ok = mbar_wait(&bars[L::bPvDone], (uint32_t)(nblk - 1) & 1u, abort_flag, status, 0x900);
     if (ok) {
       tc_fence_after();
