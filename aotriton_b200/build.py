@@ -43,7 +43,12 @@ def _nvcc() -> str:
 
 def _suffix_flags() -> list[str]:
     s = os.environ.get("AOTRITON_NAME_SUFFIX", "")
-    return [f"-DAOTRITON_NAME_SUFFIX={s}"] if s else []
+    flags = [f"-DAOTRITON_NAME_SUFFIX={s}"] if s else []
+    if os.environ.get("AB200_TRACE"):          # pipeline cycle stamps, see sm100_bwd.cu
+        flags.append("-DAB200_TRACE")
+        if os.environ.get("AB200_TRACE_TID"):
+            flags.append("-DAB200_TRACE_TID=" + os.environ["AB200_TRACE_TID"])
+    return flags
 
 
 def _digest(paths, extra: str) -> str:

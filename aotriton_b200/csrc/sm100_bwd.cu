@@ -20,7 +20,8 @@
 //   dQ, per key block i:        S = Q K_i^T        dP = dO V_i^T
 //                               dQ += dS K_i       dB = dS
 //
-// Tensor memory: [0,128) S / P, [128,256) dP / dS, [256,384) dV or dQ, [384,512) dK.
+// Tensor memory, dK/dV: [0,128) S^T, [128,256) dP^T then P^T and dS^T, [256,384) dV, [384,512) dK.
+// Tensor memory, dQ:    [0,128) S, [128,256) and [256,384) two dP / dS buffers, [384,512) dQ.
 // A warpgroup writes its packed 16-bit results into the first half of ITS OWN column range
 // (columns it has already read), so the warpgroups never overwrite each other's input;
 // the MMA issuer addresses the four pieces separately.
@@ -40,13 +41,28 @@ namespace ab200 {
 
 __device__ unsigned int g_sm100_bwd_status = 0;
 
+// Optional pipeline trace (compile with -DAB200_TRACE): SM cycle stamps of the hand-offs of the
+// first CTA of the dK/dV kernel, six per iteration, read back with ab200_debug_read_trace().
+#ifndef AB200_TRACE_TID
+#define AB200_TRACE_TID 128   // thread whose compute-side stamps are recorded
+#endif
+#ifdef AB200_TRACE
+__device__ long long g_bwd_trace[16 * 256];
+#define AB200_STAMP(iter, slot)                                                                         \
+  do {                                                                                                  \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (iter) < 256) g_bwd_trace[(iter) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define AB200_STAMP(iter, slot) do {} while (0)
+#endif
+
 namespace {
 
 using namespace ptx;
 
 constexpr int kBlk = 128;
 constexpr int kBwdThreads = 640;
-constexpr int kComputeThreads = 512;   // warps 4..19
+constexpr int kComputeWarps = 16;      // warps 4..19; each arrives on the hand-off barriers once (lane 0)
 constexpr int kWgCols = 32;            // score columns per compute warpgroup
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColDP = 128, kColAcc0 = 256, kColAcc1 = 384;
@@ -58,22 +74,25 @@ struct BwdSmem {
   static constexpr int kResA = 0, kResB = kTile;         // resident pair
   static constexpr int kRingA = 2 * kTile, kRingB = 4 * kTile;   // two stages each
   static constexpr int kAux = 6 * kTile;                 // 2 stages x (128 lse2 + 128 delta) floats
-  static constexpr int kBars = kAux + 2 * 256 * 4;
+  static constexpr int kAuxFlag = kAux + 2 * 256 * 4;    // per stage: 1 when some |lse2| is huge
+  static constexpr int kBars = kAuxFlag + 16;
   static constexpr int bResFull = 0, bRingFull = 1, bRingEmpty = 3, bAuxFull = 5, bAuxEmpty = 7, bSFull = 9,
-                       bDpFull = 10, bPFull = 11, bDsFull = 12, bAccDone = 13, bSRead = 14, bCount = 15;
+                       bDpFull = 10 /* two: one per dP buffer in the dQ kernel */, bDsFull = 12, bAccDone = 13, bSRead = 14, bCount = 15;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kDynamic = kAbort + 4 + 1024;
 };
 
+// Descriptors are built once per tile base; a k-step or a ring stage only moves the 14-bit
+// start-address field (units of 16 bytes).
 // K-major view of a [128 x HD] tile: k-step kk covers head-dim columns 16kk..16kk+15.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int kk) {
-  return smem_desc_sw128(tile_addr + (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u, 16, 1024);
+__device__ __forceinline__ uint64_t kmajor_base(uint32_t tile_addr) { return smem_desc_sw128(tile_addr, 16, 1024); }
+__device__ __forceinline__ constexpr uint32_t kmajor_step(int kk) {
+  return (uint32_t)(kk >> 2) * (16384u >> 4) + (uint32_t)(kk & 3) * (32u >> 4);
 }
 // MN-major view of the same tile: k-step kk covers rows 16kk..16kk+15, N runs over the head dim.
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int kk) {
-  return smem_desc_sw128(tile_addr + (uint32_t)kk * 2048u, 16384, 1024);
-}
+__device__ __forceinline__ uint64_t mnmajor_base(uint32_t tile_addr) { return smem_desc_sw128(tile_addr, 16384, 1024); }
+__device__ __forceinline__ constexpr uint32_t mnmajor_step(int kk) { return (uint32_t)kk * (2048u >> 4); }
 // Column of the packed 16-bit A operand for k-step kk (16 source columns = 8 packed columns):
 // each warpgroup packed its 32 source columns into the first 16 columns of its own range.
 __device__ __forceinline__ uint32_t split_a_col(int kk) { return (uint32_t)(kWgCols * (kk >> 1) + (kk & 1) * 8); }
@@ -111,15 +130,15 @@ __device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t*
   for (int s = 0; s < 2; ++s) {
     mbar_init(&bars[L::bRingFull + s], 1);
     mbar_init(&bars[L::bRingEmpty + s], 1);
-    mbar_init(&bars[L::bAuxFull + s], 32);
-    mbar_init(&bars[L::bAuxEmpty + s], kComputeThreads);
+    mbar_init(&bars[L::bAuxFull + s], 1);
+    mbar_init(&bars[L::bAuxEmpty + s], kComputeWarps);
   }
   mbar_init(&bars[L::bSFull], 1);
   mbar_init(&bars[L::bDpFull], 1);
-  mbar_init(&bars[L::bPFull], kComputeThreads);
-  mbar_init(&bars[L::bDsFull], kComputeThreads);
+  mbar_init(&bars[L::bDpFull + 1], 1);
+  mbar_init(&bars[L::bDsFull], kComputeWarps);
   mbar_init(&bars[L::bAccDone], 1);
-  mbar_init(&bars[L::bSRead], kComputeThreads);
+  mbar_init(&bars[L::bSRead], kComputeWarps);
   fence_barrier_init();
 }
 
@@ -137,6 +156,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAbort);
   float* aux = reinterpret_cast<float*>(smem + L::kAux);
+  volatile uint32_t* aux_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAuxFlag);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int z = blockIdx.z, hk = blockIdx.y, n0 = blockIdx.x * kBlk;
@@ -201,20 +221,22 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     if (lane == 0) {
       constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
       constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
-      const uint32_t k_addr = smem_u32(smem + L::kResA), v_addr = smem_u32(smem + L::kResB);
-      const uint32_t q_ring = smem_u32(smem + L::kRingA), do_ring = smem_u32(smem + L::kRingB);
+      constexpr uint32_t kStageStep = L::kTile >> 4;
+      const uint64_t k_km = kmajor_base(smem_u32(smem + L::kResA)), v_km = kmajor_base(smem_u32(smem + L::kResB));
+      const uint64_t q_km = kmajor_base(smem_u32(smem + L::kRingA)), do_km = kmajor_base(smem_u32(smem + L::kRingB));
+      const uint64_t q_mn = mnmajor_base(smem_u32(smem + L::kRingA)), do_mn = mnmajor_base(smem_u32(smem + L::kRingB));
       auto issue_s = [&](int i) {      // S^T = K Q_i^T
-        const uint32_t qa = q_ring + (uint32_t)(i & 1) * L::kTile;
+        const uint64_t qa = q_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tmem_base + kColS, desc_kmajor(k_addr, kk), desc_kmajor(qa, kk), kIdescSS, kk > 0);
+          mma_ss(tmem_base + kColS, k_km + kmajor_step(kk), qa + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
         mma_commit(&bars[L::bSFull]);
       };
       auto issue_dp = [&](int i) {     // dP^T = V dO_i^T
-        const uint32_t da = do_ring + (uint32_t)(i & 1) * L::kTile;
+        const uint64_t da = do_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tmem_base + kColDP, desc_kmajor(v_addr, kk), desc_kmajor(da, kk), kIdescSS, kk > 0);
+          mma_ss(tmem_base + kColDP, v_km + kmajor_step(kk), da + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
         mma_commit(&bars[L::bDpFull]);
       };
       bool ok = mbar_wait(&bars[L::bResFull], 0, abort_flag, status, 0x1200) &&
@@ -227,16 +249,9 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       for (int i = 0; ok && i < niter; ++i) {
         const int s = i & 1;
         const uint32_t par = (uint32_t)i & 1u;
-        if (!mbar_wait(&bars[L::bPFull], par, abort_flag, status, 0x1300 + i)) break;
-        tc_fence_after();
-        {   // dV += P^T dO_i
-          const uint32_t da = do_ring + (uint32_t)s * L::kTile;
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tmem_base + kColAcc0, tmem_base + kColS + split_a_col(kk), desc_mnmajor(da, kk), kIdescTS,
-                   (i > 0 || kk > 0) ? 1u : 0u);
-        }
         if (i + 1 < niter) {
+          // S_i sits in registers of every compute thread: its buffer can take S_{i+1} already.
+          if (!mbar_wait(&bars[L::bSRead], par, abort_flag, status, 0x1300 + i)) break;
           if (!mbar_wait(&bars[L::bRingFull + ((i + 1) & 1)], (uint32_t)((i + 1) >> 1) & 1u, abort_flag, status,
                          0x1400 + i))
             break;
@@ -244,13 +259,22 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           issue_s(i + 1);
         }
         if (!mbar_wait(&bars[L::bDsFull], par, abort_flag, status, 0x1500 + i)) break;
+        AB200_STAMP(i, 5);
         tc_fence_after();
-        {   // dK += dS^T Q_i
-          const uint32_t qa = q_ring + (uint32_t)s * L::kTile;
+        const uint32_t first = (i > 0) ? 1u : 0u;
+        {   // dV += P^T dO_i   (P^T: first 16 packed columns of each warpgroup's range of the dP buffer)
+          const uint64_t da = do_mn + (uint64_t)((uint32_t)s * kStageStep);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + split_a_col(kk), desc_mnmajor(qa, kk), kIdescTS,
-                   (i > 0 || kk > 0) ? 1u : 0u);
+            mma_ts(tmem_base + kColAcc0, tmem_base + kColDP + split_a_col(kk), da + mnmajor_step(kk), kIdescTS,
+                   kk > 0 ? 1u : first);
+        }
+        {   // dK += dS^T Q_i  (dS^T: the next 16 packed columns)
+          const uint64_t qa = q_mn + (uint64_t)((uint32_t)s * kStageStep);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + 16u + split_a_col(kk), qa + mnmajor_step(kk), kIdescTS,
+                   kk > 0 ? 1u : first);
         }
         mma_commit(&bars[L::bRingEmpty + s]);
         if (i + 1 < niter) issue_dp(i + 1);
@@ -267,14 +291,20 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       const int mbase = (mb_lo + i % nmb) * kBlk;
       const int64_t lrow = lse_offset(p, sq, h);
       float* dst = aux + s * 256;
+      bool huge = false;
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const int c = lane * 4 + t, m = mbase + c;
         const bool in = m < sq.sq;
-        dst[c] = in ? p.lse[lrow + m] * kLog2e : INFINITY;
+        const float l2 = in ? p.lse[lrow + m] * kLog2e : INFINITY;
+        dst[c] = l2;
         dst[128 + c] = in ? p.delta[lrow + m] : 0.f;
+        huge = huge || (fabsf(l2) > 1.0e6f && l2 != INFINITY);
       }
-      mbar_arrive(&bars[L::bAuxFull + s]);
+      const bool any_huge = __any_sync(0xffffffffu, huge);
+      if (lane == 0) aux_flag[s] = any_huge ? 1u : 0u;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[L::bAuxFull + s]);
     }
   } else if (warp >= 4) {
     const int quarter = warp & 3, wg = (warp - 4) >> 2;
@@ -299,32 +329,53 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       const float* dlt = lse2 + 128;
       if (!mbar_wait(&bars[L::bAuxFull + s], (uint32_t)(i >> 1) & 1u, abort_flag, status, 0x1700 + i)) { ok = false; break; }
       if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x1800 + i)) { ok = false; break; }
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 0);
       tc_fence_after();
       float pr[32];
       tmem_ld32f(tmem_base + lane_addr + kColS + cbase, pr);
       tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[L::bSRead]);
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 6);
       const bool need_mask = !(mbase >= col_lo && mbase + kWgCols - 1 <= col_hi);
       const bool any_mask = __any_sync(0xffffffffu, need_mask);
       // exponent arguments: scaled score (+ bias) minus the row's logsumexp, all in log2 units.
-      // Scale first, subtract second, so that the forward's reference point cancels exactly.
+      // Common case: one packed FMA per two elements.  With bias, or when the logsumexp is so
+      // large that product rounding matters (the aux warp flags that), scale first and subtract
+      // second, so that the forward's reference point cancels exactly.
+      if (!p.has_bias && aux_flag[s] == 0) {
+        const float2 sc2 = make_float2(p.qk_scale, p.qk_scale);
 #pragma unroll
-      for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
-      if (p.has_bias && n < sq.sk) {
-        const T* bcol = reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
-                        (int64_t)h * p.bias.s[1] + (int64_t)n * p.bias.s[3];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int m = mbase + c;
-          if (m < sq.sq) pr[c] = fmaf(to_f32<T>(bcol[(int64_t)m * p.bias.s[2]]), kLog2e, pr[c]);
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
+          const float2 a = fma2(make_float2(pr[4 * c4], pr[4 * c4 + 1]), sc2, make_float2(-l4.x, -l4.y));
+          const float2 b = fma2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]), sc2, make_float2(-l4.z, -l4.w));
+          pr[4 * c4 + 0] = ex2(a.x);
+          pr[4 * c4 + 1] = ex2(a.y);
+          pr[4 * c4 + 2] = ex2(b.x);
+          pr[4 * c4 + 3] = ex2(b.y);
         }
-      }
+      } else {
 #pragma unroll
-      for (int c4 = 0; c4 < 8; ++c4) {
-        const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
-        pr[4 * c4 + 0] = ex2(pr[4 * c4 + 0] - l4.x);
-        pr[4 * c4 + 1] = ex2(pr[4 * c4 + 1] - l4.y);
-        pr[4 * c4 + 2] = ex2(pr[4 * c4 + 2] - l4.z);
-        pr[4 * c4 + 3] = ex2(pr[4 * c4 + 3] - l4.w);
+        for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
+        if (p.has_bias && n < sq.sk) {
+          const T* bcol = reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
+                          (int64_t)h * p.bias.s[1] + (int64_t)n * p.bias.s[3];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int m = mbase + c;
+            if (m < sq.sq) pr[c] = fmaf(to_f32<T>(bcol[(int64_t)m * p.bias.s[2]]), kLog2e, pr[c]);
+          }
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
+          pr[4 * c4 + 0] = ex2(pr[4 * c4 + 0] - l4.x);
+          pr[4 * c4 + 1] = ex2(pr[4 * c4 + 1] - l4.y);
+          pr[4 * c4 + 2] = ex2(pr[4 * c4 + 2] - l4.z);
+          pr[4 * c4 + 3] = ex2(pr[4 * c4 + 3] - l4.w);
+        }
       }
       if (any_mask) {
 #pragma unroll
@@ -333,6 +384,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           pr[c] = (m >= col_lo && m <= col_hi) ? pr[c] : 0.f;
         }
       }
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 7);
       uint32_t keep = 0xffffffffu;
       if (p.dropout_on) {
         const DropoutCtx dctx = dropout_ctx(p, z, h);
@@ -342,7 +394,17 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         for (int c = 0; c < 32; ++c)
           if (dropout_keep(dctx, min(mbase + c, p.max_sq - 1), nn)) keep |= (1u << c);
       }
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 1);
+      if (!mbar_wait(&bars[L::bDpFull], par, abort_flag, status, 0x1900 + i)) { ok = false; break; }
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 2);
+      tc_fence_after();
       {
+        float dp[32];
+        tmem_ld32f(tmem_base + lane_addr + kColDP + cbase, dp);
+        tmem_wait_ld();
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 10);
+        // This thread has now read its 32 columns of dP: they can take P^T (packed, 16 columns)
+        // followed by dS^T (packed, 16 columns).
         uint32_t pk[16];
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
@@ -353,35 +415,33 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           }
           pk[c] = pack2<T>(a, b);
         }
-        tmem_st16(tmem_base + lane_addr + kColS + cbase, pk);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&bars[L::bPFull]);
-
-      if (!mbar_wait(&bars[L::bDpFull], par, abort_flag, status, 0x1900 + i)) { ok = false; break; }
-      tc_fence_after();
-      {
-        float dp[32];
-        tmem_ld32f(tmem_base + lane_addr + kColDP + cbase, dp);
-        tmem_wait_ld();
+        tmem_st16(tmem_base + lane_addr + kColDP + cbase, pk);
         if (p.dropout_on) {
 #pragma unroll
           for (int c = 0; c < 32; ++c) dp[c] = ((keep >> c) & 1u) ? dp[c] * p.dropout_scale : 0.f;
         }
-        uint32_t pk[16];
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
           const float4 d4 = *reinterpret_cast<const float4*>(dlt + 4 * c4);
-          pk[2 * c4] = pack2<T>(pr[4 * c4] * (dp[4 * c4] - d4.x), pr[4 * c4 + 1] * (dp[4 * c4 + 1] - d4.y));
-          pk[2 * c4 + 1] = pack2<T>(pr[4 * c4 + 2] * (dp[4 * c4 + 2] - d4.z), pr[4 * c4 + 3] * (dp[4 * c4 + 3] - d4.w));
+          const float2 a = mul2(make_float2(pr[4 * c4], pr[4 * c4 + 1]),
+                                sub2(make_float2(dp[4 * c4], dp[4 * c4 + 1]), make_float2(d4.x, d4.y)));
+          const float2 b = mul2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]),
+                                sub2(make_float2(dp[4 * c4 + 2], dp[4 * c4 + 3]), make_float2(d4.z, d4.w)));
+          pk[2 * c4] = pack2<T>(a.x, a.y);
+          pk[2 * c4 + 1] = pack2<T>(b.x, b.y);
         }
-        tmem_st16(tmem_base + lane_addr + kColDP + cbase, pk);
+        tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16, pk);
       }
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 11);
       tmem_wait_st();
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 12);
       tc_fence_before();
-      mbar_arrive(&bars[L::bDsFull]);
-      mbar_arrive(&bars[L::bAuxEmpty + s]);
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bars[L::bDsFull]);
+        mbar_arrive(&bars[L::bAuxEmpty + s]);
+      }
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 3);
     }
     if (ok) ok = mbar_wait(&bars[L::bAccDone], 0, abort_flag, status, 0x1A00);
     if (ok && wg < HD / 32) {
@@ -485,21 +545,24 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     if (lane == 0) {
       constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
       constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
-      const uint32_t q_addr = smem_u32(smem + L::kResA), do_addr = smem_u32(smem + L::kResB);
-      const uint32_t k_ring = smem_u32(smem + L::kRingA), v_ring = smem_u32(smem + L::kRingB);
+      constexpr uint32_t kStageStep = L::kTile >> 4;
+      const uint64_t q_km = kmajor_base(smem_u32(smem + L::kResA)), do_km = kmajor_base(smem_u32(smem + L::kResB));
+      const uint64_t k_km = kmajor_base(smem_u32(smem + L::kRingA)), v_km = kmajor_base(smem_u32(smem + L::kRingB));
+      const uint64_t k_mn = mnmajor_base(smem_u32(smem + L::kRingA));
       auto issue_s = [&](int i) {      // S = Q K_i^T
-        const uint32_t ka = k_ring + (uint32_t)(i & 1) * L::kTile;
+        const uint64_t ka = k_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tmem_base + kColS, desc_kmajor(q_addr, kk), desc_kmajor(ka, kk), kIdescSS, kk > 0);
+          mma_ss(tmem_base + kColS, q_km + kmajor_step(kk), ka + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
         mma_commit(&bars[L::bSFull]);
       };
-      auto issue_dp = [&](int i) {     // dP = dO V_i^T
-        const uint32_t va = v_ring + (uint32_t)(i & 1) * L::kTile;
+      auto issue_dp = [&](int i) {     // dP = dO V_i^T, into dP buffer i & 1
+        const uint64_t va = v_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
+        const uint32_t d = tmem_base + kColDP + (uint32_t)(i & 1) * 128u;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tmem_base + kColDP, desc_kmajor(do_addr, kk), desc_kmajor(va, kk), kIdescSS, kk > 0);
-        mma_commit(&bars[L::bDpFull]);
+          mma_ss(d, do_km + kmajor_step(kk), va + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
+        mma_commit(&bars[L::bDpFull + (i & 1)]);
       };
       bool ok = mbar_wait(&bars[L::bResFull], 0, abort_flag, status, 0x2200) &&
                 mbar_wait(&bars[L::bRingFull + 0], 0, abort_flag, status, 0x2201);
@@ -519,18 +582,21 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
             break;
           tc_fence_after();
           issue_s(i + 1);
+          // The other dP buffer held dS_{i-1}, which dQ_{i-1} (issued earlier) consumes first.
+          issue_dp(i + 1);
         }
         if (!mbar_wait(&bars[L::bDsFull], par, abort_flag, status, 0x2500 + i)) break;
         tc_fence_after();
         {   // dQ += dS K_i
-          const uint32_t ka = k_ring + (uint32_t)s * L::kTile;
+          const uint64_t ka = k_mn + (uint64_t)((uint32_t)s * kStageStep);
+          const uint32_t first = (i > 0) ? 1u : 0u;
+          const uint32_t ds_col = tmem_base + kColDP + (uint32_t)s * 128u;
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tmem_base + kColAcc0, tmem_base + kColDP + split_a_col(kk), desc_mnmajor(ka, kk), kIdescTS,
-                   (i > 0 || kk > 0) ? 1u : 0u);
+            mma_ts(tmem_base + kColAcc1, ds_col + split_a_col(kk), ka + mnmajor_step(kk), kIdescTS,
+                   kk > 0 ? 1u : first);
         }
         mma_commit(&bars[L::bRingEmpty + s]);
-        if (i + 1 < niter) issue_dp(i + 1);
       }
       mma_commit(&bars[L::bAccDone]);
     }
@@ -551,6 +617,9 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     const int64_t lrow = lse_offset(p, sq, h);
     const float lse2 = (m < sq.sq) ? p.lse[lrow + m] * kLog2e : INFINITY;
     const float dlt = (m < sq.sq) ? p.delta[lrow + m] : 0.f;
+    // one packed FMA per two elements unless bias is present or the logsumexp is so large that
+    // product rounding matters (then: scale first, subtract second, like the forward)
+    const bool simple = !p.has_bias && !__any_sync(0xffffffffu, fabsf(lse2) > 1.0e6f && lse2 != INFINITY);
     DropoutCtx dctx;
     if (p.dropout_on) dctx = dropout_ctx(p, z, h);
     const int mm = min(m, sq.sq - 1);
@@ -570,20 +639,31 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       tmem_ld32f(tmem_base + lane_addr + kColS + cbase, pr);
       tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(&bars[L::bSRead]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[L::bSRead]);
       const bool need_mask = !(nbase >= row_lo && nbase + kWgCols - 1 <= row_hi);
       const bool any_mask = __any_sync(0xffffffffu, need_mask);
+      if (simple) {
+        const float2 sc2 = make_float2(p.qk_scale, p.qk_scale), nl2 = make_float2(-lse2, -lse2);
 #pragma unroll
-      for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
-      if (p.has_bias) {
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int n = nbase + c;
-          if (n < sq.sk) pr[c] = fmaf(to_f32<T>(bias_row[(int64_t)n * p.bias.s[3]]), kLog2e, pr[c]);
+        for (int c = 0; c < 32; c += 2) {
+          const float2 a = fma2(make_float2(pr[c], pr[c + 1]), sc2, nl2);
+          pr[c] = ex2(a.x);
+          pr[c + 1] = ex2(a.y);
         }
-      }
+      } else {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) pr[c] = ex2(pr[c] - lse2);
+        for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
+        if (p.has_bias) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int n = nbase + c;
+            if (n < sq.sk) pr[c] = fmaf(to_f32<T>(bias_row[(int64_t)n * p.bias.s[3]]), kLog2e, pr[c]);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 32; ++c) pr[c] = ex2(pr[c] - lse2);
+      }
       if (any_mask) {
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
@@ -598,20 +678,24 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) keep |= dropout_keep4(dctx, md, (nbase >> 2) + c4) << (4 * c4);
       }
-      if (!mbar_wait(&bars[L::bDpFull], par, abort_flag, status, 0x2700 + i)) { ok = false; break; }
+      const uint32_t dp_col = tmem_base + lane_addr + kColDP + (uint32_t)(i & 1) * 128u + cbase;
+      if (!mbar_wait(&bars[L::bDpFull + (i & 1)], (uint32_t)(i >> 1) & 1u, abort_flag, status, 0x2700 + i)) { ok = false; break; }
       tc_fence_after();
       {
         float dp[32];
-        tmem_ld32f(tmem_base + lane_addr + kColDP + cbase, dp);
+        tmem_ld32f(dp_col, dp);
         tmem_wait_ld();
         if (p.dropout_on) {
 #pragma unroll
           for (int c = 0; c < 32; ++c) dp[c] = ((keep >> c) & 1u) ? dp[c] * p.dropout_scale : 0.f;
         }
         uint32_t pk[16];
+        const float2 dl2 = make_float2(dlt, dlt);
 #pragma unroll
-        for (int c = 0; c < 16; ++c)
-          pk[c] = pack2<T>(pr[2 * c] * (dp[2 * c] - dlt), pr[2 * c + 1] * (dp[2 * c + 1] - dlt));
+        for (int c = 0; c < 16; ++c) {
+          const float2 a = mul2(make_float2(pr[2 * c], pr[2 * c + 1]), sub2(make_float2(dp[2 * c], dp[2 * c + 1]), dl2));
+          pk[c] = pack2<T>(a.x, a.y);
+        }
         if (p.has_dbias && m < sq.sq) {
           // dB = cast(dS): the packed pairs are exactly the values to store
           if (p.dbias.s[3] == 1 && nbase + 32 <= sq.sk && (reinterpret_cast<uintptr_t>(db_row + nbase) & 15u) == 0) {
@@ -630,11 +714,12 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
             }
           }
         }
-        tmem_st16(tmem_base + lane_addr + kColDP + cbase, pk);
+        tmem_st16(dp_col, pk);
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&bars[L::bDsFull]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[L::bDsFull]);
     }
     if (ok) ok = mbar_wait(&bars[L::bAccDone], 0, abort_flag, status, 0x2800);
     if (ok && wg < HD / 32) {
@@ -643,7 +728,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
                (sq.q0 + m) * p.dq.s[2];
       float v[32];
       const int d0 = wg * 32;
-      tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
+      tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
       tmem_wait_ld();
       if (m < sq.sq) store_row_chunk32<T>(dqp, v, p.sm_scale, d0, p.dqk);
     }
@@ -706,6 +791,12 @@ bool sm100_bwd_supported(int dtype, const Params& p) {
 
 cudaError_t launch_sm100_bwd_dkdv(int dtype, const Params& p, cudaStream_t st) { return launch_bwd(1, dtype, p, st); }
 cudaError_t launch_sm100_bwd_dq(int dtype, const Params& p, cudaStream_t st) { return launch_bwd(2, dtype, p, st); }
+
+#ifdef AB200_TRACE
+extern "C" __attribute__((visibility("default"))) int ab200_debug_read_trace(long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, g_bwd_trace, sizeof(long long) * (size_t)(n < 4096 ? n : 4096));
+}
+#endif
 
 unsigned int sm100_bwd_status(bool reset) {
   unsigned int v = 0;

@@ -120,7 +120,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars[L::bSFull + s], 1);
-      mbar_init(&bars[L::bPFull + s], 128);
+      mbar_init(&bars[L::bPFull + s], 4);      // one arrival per softmax warp
     }
     mbar_init(&bars[L::bPvDone], 1);
     fence_barrier_init();
@@ -178,20 +178,24 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
     if (lane == 0) {
       constexpr uint32_t kIdescQK = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
       constexpr uint32_t kIdescPV = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
-      const uint32_t q_addr = smem_u32(smem + L::kQ);
-      const uint32_t k_addr = smem_u32(smem + L::kK);
-      const uint32_t v_addr = smem_u32(smem + L::kV);
+      // Descriptors are built once; a k-step or a ring stage only moves the 14-bit start-address
+      // field (units of 16 bytes), which cannot carry out of the field for in-range addresses.
+      const uint64_t q_desc = smem_desc_sw128(smem_u32(smem + L::kQ), 16, 1024);
+      const uint64_t k_desc = smem_desc_sw128(smem_u32(smem + L::kK), 16, 1024);
+      const uint64_t v_desc = smem_desc_sw128(smem_u32(smem + L::kV), 16384, 1024);
+      constexpr uint32_t kStageStep = L::kTileBytes >> 4;
       bool ok = mbar_wait(&bars[L::bQFull], 0, abort_flag, status, 0x300);
       auto issue_qk = [&](int j) -> bool {
         const int s = j % kStages;
         if (!mbar_wait(&bars[L::bKFull + s], (uint32_t)(j / kStages) & 1u, abort_flag, status, 0x400 + j)) return false;
         tc_fence_after();
         const uint32_t d = tmem_base + (uint32_t)(j & 1) * 128u;
+        const uint64_t kd = k_desc + (uint64_t)((uint32_t)s * kStageStep);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u;
-          mma_ss(d, smem_desc_sw128(q_addr + off, 16, 1024),
-                 smem_desc_sw128(k_addr + (uint32_t)s * L::kTileBytes + off, 16, 1024), kIdescQK, kk > 0);
+          constexpr uint32_t kHalfStep = 16384u >> 4, kInner = 32u >> 4;
+          const uint32_t off = (uint32_t)(kk >> 2) * kHalfStep + (uint32_t)(kk & 3) * kInner;
+          mma_ss(d, q_desc + off, kd + off, kIdescQK, kk > 0 ? 1u : 0u);
         }
         mma_commit(&bars[L::bKEmpty + s]);
         mma_commit(&bars[L::bSFull + (j & 1)]);
@@ -207,12 +211,12 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         if (!mbar_wait(&bars[L::bVFull + s], (uint32_t)(j / kStages) & 1u, abort_flag, status, 0x600 + j)) break;
         tc_fence_after();
         const uint32_t pcol = tmem_base + (uint32_t)(j & 1) * 128u;
+        const uint64_t vd = v_desc + (uint64_t)((uint32_t)s * kStageStep);
+        const uint32_t first = (j > 0) ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk) {
           // 16 keys per step: 8 packed columns of P, 2048 bytes of V (two 8-key groups)
-          mma_ts(tmem_o, pcol + (uint32_t)kk * 8u,
-                 smem_desc_sw128(v_addr + (uint32_t)s * L::kTileBytes + (uint32_t)kk * 2048u, 16384, 1024), kIdescPV,
-                 (j > 0 || kk > 0) ? 1u : 0u);
+          mma_ts(tmem_o, pcol + (uint32_t)kk * 8u, vd + (uint32_t)kk * (2048u >> 4), kIdescPV, kk > 0 ? 1u : first);
         }
         mma_commit(&bars[L::bVEmpty + s]);
         mma_commit(&bars[L::bPvDone]);
@@ -269,10 +273,10 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         }
         float m8[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) m8[c] = sc[c];
+        for (int c = 0; c < 8; ++c) m8[c] = fmaxf(sc[2 * c], sc[2 * c + 1]);
 #pragma unroll
-        for (int c = 8; c < 128; ++c) m8[c & 7] = fmaxf(m8[c & 7], sc[c]);
-        mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+        for (int c = 16; c < 128; c += 2) m8[(c >> 1) & 7] = fmax3(m8[(c >> 1) & 7], sc[c], sc[c + 1]);
+        mx = fmaxf(fmax3(m8[0], m8[1], m8[2]), fmaxf(fmax3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7])));
         mx *= p.qk_scale;
         const bool huge = fabsf(mx) > 1.0e6f && mx != -INFINITY;
         if (__any_sync(0xffffffffu, huge)) simple = false;
@@ -295,10 +299,10 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         }
         float m8[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) m8[c] = sc[c];
+        for (int c = 0; c < 8; ++c) m8[c] = fmaxf(sc[2 * c], sc[2 * c + 1]);
 #pragma unroll
-        for (int c = 8; c < 128; ++c) m8[c & 7] = fmaxf(m8[c & 7], sc[c]);
-        mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+        for (int c = 16; c < 128; c += 2) m8[(c >> 1) & 7] = fmax3(m8[(c >> 1) & 7], sc[c], sc[c + 1]);
+        mx = fmaxf(fmax3(m8[0], m8[1], m8[2]), fmaxf(fmax3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7])));
       }
       // Advance the reference maximum only when it moved by more than the threshold.
       const bool grow = mx > m_used + kRescaleThreshold;     // false when mx == -inf
@@ -324,24 +328,29 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       }
       l *= alpha;
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-      float s8[8];
+      float2 s4[4];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) s8[c] = 0.f;
+      for (int c = 0; c < 4; ++c) s4[c] = make_float2(0.f, 0.f);
       if (simple) {
-        const float neg_m = -m_safe;
+        const float2 sc2 = make_float2(p.qk_scale, p.qk_scale), nm2 = make_float2(-m_safe, -m_safe);
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          sc[c] = ex2(fmaf(sc[c], p.qk_scale, neg_m));
-          s8[c & 7] += sc[c];
+        for (int c = 0; c < 128; c += 2) {
+          const float2 a = fma2(make_float2(sc[c], sc[c + 1]), sc2, nm2);
+          sc[c] = ex2(a.x);
+          sc[c + 1] = ex2(a.y);
+          s4[(c >> 1) & 3] = add2(s4[(c >> 1) & 3], make_float2(sc[c], sc[c + 1]));
         }
       } else {
+        const float2 nm2 = make_float2(-m_safe, -m_safe);
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          sc[c] = ex2(sc[c] - m_safe);
-          s8[c & 7] += sc[c];
+        for (int c = 0; c < 128; c += 2) {
+          const float2 a = add2(make_float2(sc[c], sc[c + 1]), nm2);
+          sc[c] = ex2(a.x);
+          sc[c + 1] = ex2(a.y);
+          s4[(c >> 1) & 3] = add2(s4[(c >> 1) & 3], make_float2(sc[c], sc[c + 1]));
         }
       }
-      const float sum = ((s8[0] + s8[1]) + (s8[2] + s8[3])) + ((s8[4] + s8[5]) + (s8[6] + s8[7]));
+      const float sum = ((s4[0].x + s4[0].y) + (s4[1].x + s4[1].y)) + ((s4[2].x + s4[2].y) + (s4[3].x + s4[3].y));
       l += sum;
       if (p.dropout_on) {
         const int mm = min(m, p.max_sq - 1);
@@ -363,7 +372,8 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&bars[L::bPFull + sb]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[L::bPFull + sb]);
     }
     // ---- epilogue ---------------------------------------------------------------------
     // Holding S of the last block only guarantees that P V of all blocks but the last two has

@@ -29,14 +29,18 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// One try: returns true when the phase with this parity has completed.  The hardware may park
+// the thread for up to `kSuspendHintNs` while the phase is still pending, and wakes it when the
+// phase completes, so waiting costs few issue slots and no wake-up latency.
+constexpr uint32_t kSuspendHintNs = 1000000u;   // 1 ms
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
@@ -52,12 +56,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
                                           unsigned int* status, uint32_t where) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  for (uint32_t i = 1;; ++i) {
+  for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) break;
-    }
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) break;
   }
   *abort_flag = 1u;
   if (status) atomicCAS(status, 0u, where);
@@ -67,8 +69,49 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // Bounded wait without side effects, for draining copies on the failure path.
 __device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity) {
   const long long t0 = clock64();
-  for (uint32_t i = 1; !mbar_try_wait(bar, parity); ++i)
-    if ((i & 255u) == 0u && clock64() - t0 > kWaitLimitCycles) return;
+  while (!mbar_try_wait(bar, parity))
+    if (clock64() - t0 > kWaitLimitCycles) return;
+}
+
+// Packed pairs of fp32 operations (one instruction for two lanes of work on sm_100).
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "sub.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+// max of three (one instruction on sm_100).
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
 // 2^x on the special-function unit (flushes denormals; -inf -> 0).
