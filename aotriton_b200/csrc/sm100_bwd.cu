@@ -368,6 +368,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
             if (m < sq.sq) pr[c] = fmaf(to_f32<T>(bcol[(int64_t)m * p.bias.s[2]]), kLog2e, pr[c]);
           }
         }
+        __syncwarp();   // lanes beyond the sequence skipped the loads
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
           const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
@@ -455,6 +456,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
       tmem_wait_ld();
       if (n < sq.sk) store_row_chunk32<T>(dvp, v, 1.0f, d0, p.dvo);
+      __syncwarp();
       tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
       tmem_wait_ld();
       if (n < sq.sk) store_row_chunk32<T>(dkp, v, p.sm_scale, d0, p.dqk);
@@ -582,8 +584,6 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
             break;
           tc_fence_after();
           issue_s(i + 1);
-          // The other dP buffer held dS_{i-1}, which dQ_{i-1} (issued earlier) consumes first.
-          issue_dp(i + 1);
         }
         if (!mbar_wait(&bars[L::bDsFull], par, abort_flag, status, 0x2500 + i)) break;
         tc_fence_after();
@@ -597,6 +597,9 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
                    kk > 0 ? 1u : first);
         }
         mma_commit(&bars[L::bRingEmpty + s]);
+        // dP_{i+1} goes behind dQ_i: issued ahead of it (the second dP buffer would allow that)
+        // it delays dQ_i and the release of the K/V stage, which measured slower.
+        if (i + 1 < niter) issue_dp(i + 1);
       }
       mma_commit(&bars[L::bAccDone]);
     }
@@ -696,6 +699,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
           const float2 a = mul2(make_float2(pr[2 * c], pr[2 * c + 1]), sub2(make_float2(dp[2 * c], dp[2 * c + 1]), dl2));
           pk[c] = pack2<T>(a.x, a.y);
         }
+        tmem_st16(dp_col, pk);
         if (p.has_dbias && m < sq.sq) {
           // dB = cast(dS): the packed pairs are exactly the values to store
           if (p.dbias.s[3] == 1 && nbase + 32 <= sq.sk && (reinterpret_cast<uintptr_t>(db_row + nbase) & 15u) == 0) {
@@ -714,8 +718,8 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
             }
           }
         }
-        tmem_st16(dp_col, pk);
       }
+      __syncwarp();   // the dB stores diverge; TMEM instructions are warp-collective
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();

@@ -405,6 +405,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
             }
           }
         }
+        __syncwarp();   // the stores diverge on ragged tiles; TMEM loads are warp-collective
       }
       if (p.lse != nullptr && m < sq.sq)
         p.lse[lse_offset(p, sq, h) + m] = (l > 0.f) ? (m_used + log2f(l)) * kLn2 : INFINITY;
