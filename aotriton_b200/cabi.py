@@ -15,10 +15,11 @@ DTYPE_FP32, DTYPE_FP16, DTYPE_BF16 = 1, 2, 3
 CAUSAL_NONE, CAUSAL_WINDOWED = 0, 3
 WINDOW_TOP_LEFT, WINDOW_BOTTOM_RIGHT = -2147483647, -2147483646
 VARLEN_NONE, VARLEN_COMPACT, VARLEN_PADDED, VARLEN_STRIDED = 0, 1, 2, 3
+STATIC_DELTA_FLOATS = 1 << 20   # AB200_STATIC_DELTA_FLOATS
 
 # Exported symbols, in header order (checked by the CPU test-suite).
 SYMBOLS = [
-    "ab200_attn_fwd", "ab200_attn_bwd", "ab200_bwd_preprocess", "ab200_bwd_dkdv", "ab200_bwd_dq",
+    "ab200_attn_fwd", "ab200_attn_bwd", "ab200_attn_bwd_static_scratch", "ab200_bwd_preprocess", "ab200_bwd_dkdv", "ab200_bwd_dq",
     "ab200_debug_simulate_encoded_softmax", "ab200_check_gpu", "ab200_multiprocessor_count",
     "ab200_set_kernel_family", "ab200_last_fwd_family", "ab200_last_bwd_family", "ab200_kernel_status",
     "ab200_launch_count",
@@ -72,7 +73,8 @@ def lib() -> C.CDLL:
         L = C.CDLL(str(LIB_PATH))
         for name in ("ab200_attn_fwd",):
             getattr(L, name).argtypes = [C.POINTER(FwdArgs), C.c_void_p]
-        for name in ("ab200_attn_bwd", "ab200_bwd_preprocess", "ab200_bwd_dkdv", "ab200_bwd_dq"):
+        for name in ("ab200_attn_bwd", "ab200_attn_bwd_static_scratch", "ab200_bwd_preprocess", "ab200_bwd_dkdv",
+                     "ab200_bwd_dq"):
             getattr(L, name).argtypes = [C.POINTER(BwdArgs), C.c_void_p]
         L.ab200_debug_simulate_encoded_softmax.argtypes = [
             C.POINTER(View4), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
@@ -165,7 +167,7 @@ def make_bwd_args(q, k, v, out, dout, dq, dk, dv, lse, delta, *, bias=None, dbia
 def attn_bwd(q, k, v, out, dout, dq, dk, dv, lse, delta, *, stream=None, stage="all", **kw) -> int:
     a = make_bwd_args(q, k, v, out, dout, dq, dk, dv, lse, delta, **kw)
     fn = {"all": "ab200_attn_bwd", "preprocess": "ab200_bwd_preprocess", "dkdv": "ab200_bwd_dkdv",
-          "dq": "ab200_bwd_dq"}[stage]
+          "dq": "ab200_bwd_dq", "static_scratch": "ab200_attn_bwd_static_scratch"}[stage]
     return getattr(lib(), fn)(C.byref(a), stream if stream is not None else current_stream_handle())
 
 

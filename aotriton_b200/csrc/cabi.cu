@@ -256,6 +256,58 @@ int ab200_attn_bwd(const ab200_attn_bwd_args* a, void* stream) {
   return ab200_bwd_dq(a, stream);
 }
 
+// --- backward with the delta scratch inside the library image -----------------------------
+// For hosts that have no device memory left to lend and no allocator to call back into.  The
+// array below is what `args->delta` would otherwise point to.  In host code its name is only a
+// handle: the device address is looked up once per device with cudaGetSymbolAddress and cached.
+static __device__ __align__(256) float g_static_delta[AB200_STATIC_DELTA_FLOATS];
+
+namespace {
+// Device address of g_static_delta on `dev`, which must be the current device; nullptr on error.
+float* static_delta_address(int dev, cudaError_t* err) {
+  static std::mutex mu;
+  static float* table[64] = {};
+  *err = cudaSuccess;
+  if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
+  std::lock_guard<std::mutex> lock(mu);
+  if (table[dev] == nullptr) {
+    int cur = -1;
+    if ((*err = cudaGetDevice(&cur)) != cudaSuccess) return nullptr;
+    if (cur != dev) { *err = cudaErrorInvalidDevice; return nullptr; }   // symbol lookup is per current device
+    float* ptr = nullptr;
+    if ((*err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_delta)) != cudaSuccess) return nullptr;
+    table[dev] = ptr;
+  }
+  return table[dev];
+}
+}  // namespace
+
+int ab200_attn_bwd_static_scratch(const ab200_attn_bwd_args* a, void* stream) {
+  if (a == nullptr) return kErrInvalidValue;
+  if (!a->dq.ptr || !a->dk.ptr || !a->dv.ptr) return kErrInvalidValue;
+  const ab200_attn_problem& pr = a->prob;
+  // Rows of the logsumexp / delta matrix: dense and padded layouts are (batch*Hq, max_sq);
+  // token-packed varlen is (Hq, tokens in the packed q tensor).
+  const bool packed = pr.cu_seqlens_q != nullptr && pr.varlen_type != AB200_VARLEN_PADDED;
+  const long long need = packed ? (long long)pr.num_head_q * (long long)a->q.size[2]
+                                : (long long)pr.batch * (long long)pr.num_head_q * (long long)pr.max_seqlen_q;
+  if (need < 0 || need > (long long)AB200_STATIC_DELTA_FLOATS) {
+    std::fprintf(stderr,
+                 "[aotriton_b200] ab200_attn_bwd_static_scratch: delta needs %lld floats, the built-in scratch "
+                 "holds %u; use ab200_attn_bwd with a caller-provided delta buffer\n",
+                 need, (unsigned)AB200_STATIC_DELTA_FLOATS);
+    return kErrInvalidValue;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int e = check_device(st)) return e;
+  cudaError_t cerr;
+  float* delta = static_delta_address(stream_device(st), &cerr);
+  if (delta == nullptr) return (int)cerr;
+  ab200_attn_bwd_args b = *a;
+  b.delta = delta;
+  return ab200_attn_bwd(&b, stream);
+}
+
 // --- HIP-named runtime helpers used by the Python tests of the reference
 // (bindings/hipruntime.cc:92-93).  CUDA and HIP number their common errors alike.
 AB200_API int hipGetLastError(void) { return (int)cudaGetLastError(); }

@@ -122,6 +122,32 @@ AB200_API int ab200_attn_fwd(const ab200_attn_fwd_args* args, void* stream);
  * (modules/flash/csrc/attn_bwd.cc:56-160: bwd_preprocess, bwd_kernel_dk_dv, bwd_kernel_dq). */
 AB200_API int ab200_attn_bwd(const ab200_attn_bwd_args* args, void* stream);
 
+/*
+ * Backward for callers that can neither hand the library a delta buffer nor let it ask an
+ * allocator for one.  This entry point has no counterpart in the reference, whose backward
+ * always obtains delta through the caller's LazyTensor allocator callback.
+ *
+ * Who needs it: hosts that planned all device memory up front and have none left to give
+ * (fixed-arena inference or training runtimes), and FFI callers (C, Go, Java ...) that have
+ * no device allocator to wire into a callback.  For them `args->delta` is ignored; delta
+ * lives in a fixed array inside the library image instead (AB200_STATIC_DELTA_FLOATS floats
+ * = 4 MiB, resident on every GPU that loads the library until the process exits).
+ *
+ *   - Limit: the logsumexp/delta matrix of the call (batch * num_head_q * max_seqlen_q
+ *     floats; for token-packed varlen num_head_q * q.size[2]) must fit in the array,
+ *     otherwise the call returns hipErrorInvalidValue (1), prints one line naming the limit
+ *     to stderr, and launches nothing.
+ *   - The first call on each device looks up the array's device address; make that call
+ *     with the device current and before any stream capture begins.  Later calls only launch.
+ *   - Nothing is allocated or freed here, by the CUDA runtime or any other library.
+ *   - All calls share the one array.  Each call overwrites the part it uses before reading
+ *     it, so leftovers of earlier calls are harmless, but two calls whose kernels overlap on
+ *     the GPU (different streams, no dependency) race on it: serialise them.
+ * Everything else (inputs, outputs, return codes, asynchrony) is as for ab200_attn_bwd.
+ */
+#define AB200_STATIC_DELTA_FLOATS (1u << 20)
+AB200_API int ab200_attn_bwd_static_scratch(const ab200_attn_bwd_args* args, void* stream);
+
 /* The three backward stages one by one (modules/flash/kernel/bwd_preprocess.py:28-250,
  * bwd_kernel_dk_dv.py:48-417, bwd_kernel_dq.py:45-389). */
 AB200_API int ab200_bwd_preprocess(const ab200_attn_bwd_args* args, void* stream);
