@@ -1,5 +1,5 @@
 // Thin inline-PTX layer for the Blackwell (sm_100a) execution model: mbarriers with
-// bounded waits, TMA tile loads (never multicast), tensor memory (TMEM) management,
+// bounded waits, TMA tile loads (each CTA fetches its own tiles), tensor memory (TMEM) management,
 // tcgen05 MMA issue/commit, TMEM loads/stores, and the shared-memory / instruction
 // descriptors those need.  Nothing here allocates or synchronises on its own.
 #pragma once
