@@ -369,37 +369,66 @@ __global__ void __launch_bounds__(kThreads) general_bwd_dq_kernel(const __grid_c
 }
 
 // ---------------------------------------------------------------------------
-// delta[m] = sum_d O[m,d] * dO[m,d] in fp32, written with the LSE layout.
-// One warp per row; grid = (cdiv(max_sq, rows per CTA), Hq, batch).  HBM-bound.
+// delta[m] = sum_d O[m,d] * dO[m,d] in fp32, written with the LSE layout.  HBM-bound.
+// grid = (cdiv(max_sq, 128), Hq, batch); a CTA of 8 warps owns 128 rows of one (sequence, head).
+// Fast path (16-bit types, D in {64,128,256}, 16-byte aligned rows): D/8 lanes share a row with
+// one 16-byte load each from O and dO, four rows in flight per lane group.  Otherwise one warp
+// per row with scalar loads.
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const __grid_constant__ Params p) {
   const int z = blockIdx.z, h = blockIdx.y;
   const Seq sq = resolve_seq(p, z);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int d = p.dvo;
-  const bool vec_ok = (sizeof(T) == 2) && (d % 8 == 0) &&
+  const int row0 = blockIdx.x * 128;
+  if (row0 >= sq.sq) return;
+  const int64_t lrow = lse_offset(p, sq, h);
+  const bool vec_ok = (sizeof(T) == 2) && (d == 64 || d == 128 || d == 256) &&
                       ((reinterpret_cast<uintptr_t>(p.out.ptr) | reinterpret_cast<uintptr_t>(p.dout.ptr)) % 16 == 0) &&
                       (p.out.s[0] % 8 == 0) && (p.out.s[1] % 8 == 0) && (p.out.s[2] % 8 == 0) &&
                       (p.dout.s[0] % 8 == 0) && (p.dout.s[1] % 8 == 0) && (p.dout.s[2] % 8 == 0);
-  for (int m = blockIdx.x * 32 + warp; m < min(sq.sq, (int)(blockIdx.x + 1) * 32); m += 8) {
+  if (vec_ok) {
+    const int lpr = d >> 3;                 // lanes per row: 8, 16 or 32
+    const int rpw = 32 / lpr;               // rows per warp pass
+    const int sub = lane / lpr, col = (lane % lpr) * 8;
+    // warp w covers rows row0 + 16w .. +15 in passes of rpw rows, four passes in flight
+    const int wrow0 = row0 + warp * 16;
+    for (int pass = 0; pass < 16 / rpw; pass += 4) {
+      uint4 a[4], b[4];
+      int rows[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        rows[u] = wrow0 + (pass + u) * rpw + sub;
+        const bool in = (pass + u) * rpw < 16 && rows[u] < sq.sq;
+        if (in) {
+          a[u] = *reinterpret_cast<const uint4*>(row_ptr<T>(p.out, sq.bidx, h, sq.q0 + rows[u]) + col);
+          b[u] = *reinterpret_cast<const uint4*>(row_ptr<T>(p.dout, sq.bidx, h, sq.q0 + rows[u]) + col);
+        } else {
+          a[u] = make_uint4(0, 0, 0, 0);
+          b[u] = make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const T* ae = reinterpret_cast<const T*>(&a[u]);
+        const T* be = reinterpret_cast<const T*>(&b[u]);
+        float acc = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc = fmaf(to_f32<T>(ae[e]), to_f32<T>(be[e]), acc);
+        for (int o = lpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if ((lane % lpr) == 0 && (pass + u) * rpw < 16 && rows[u] < sq.sq) p.delta[lrow + rows[u]] = acc;
+      }
+    }
+    return;
+  }
+  for (int m = row0 + warp; m < min(sq.sq, row0 + 128); m += 8) {
     const T* op = row_ptr<T>(p.out, sq.bidx, h, sq.q0 + m);
     const T* gp = row_ptr<T>(p.dout, sq.bidx, h, sq.q0 + m);
     float acc = 0.f;
-    if (vec_ok) {
-      for (int c = lane * 8; c < d; c += 256) {
-        uint4 a = *reinterpret_cast<const uint4*>(op + c);
-        uint4 b = *reinterpret_cast<const uint4*>(gp + c);
-        const T* ae = reinterpret_cast<const T*>(&a);
-        const T* be = reinterpret_cast<const T*>(&b);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc = fmaf(to_f32<T>(ae[e]), to_f32<T>(be[e]), acc);
-      }
-    } else {
-      for (int c = lane; c < d; c += 32) acc = fmaf(to_f32<T>(op[c]), to_f32<T>(gp[c]), acc);
-    }
+    for (int c = lane; c < d; c += 32) acc = fmaf(to_f32<T>(op[c]), to_f32<T>(gp[c]), acc);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) p.delta[lse_offset(p, sq, h) + m] = acc;
+    if (lane == 0) p.delta[lrow + m] = acc;
   }
 }
 
@@ -485,7 +514,7 @@ cudaError_t launch_general(int which, int dtype, const Params& p, cudaStream_t s
 
 cudaError_t launch_preprocess(int dtype, const Params& p, cudaStream_t st) {
   if (p.max_sq <= 0 || p.batch <= 0) return cudaSuccess;
-  dim3 grid((p.max_sq + 31) / 32, p.hq, p.batch);
+  dim3 grid((p.max_sq + 127) / 128, p.hq, p.batch);
   switch (dtype) {
     case 1: bwd_preprocess_kernel<float><<<grid, 256, 0, st>>>(p); break;
     case 2: bwd_preprocess_kernel<__half><<<grid, 256, 0, st>>>(p); break;

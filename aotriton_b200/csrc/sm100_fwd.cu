@@ -1,21 +1,26 @@
 // Forward attention on the 5th-generation tensor cores (tcgen05) of sm_100a.
 //
-// One CTA owns a tile of 128 query rows of one (sequence, q-head) and walks the key/value
-// blocks (128 keys each) its window can reach.  Six warps, three roles:
+// One CTA owns TWO tiles of 128 query rows (256 consecutive rows) of one (sequence, q-head) and
+// walks the key/value blocks (128 keys each) their window can reach; each K/V block is loaded
+// once and used by both tiles.  Twelve warps:
 //
-//   warp 0      TMA producer   Q once, then K and V blocks through two 2-stage rings
-//                              (cp.async.bulk.tensor, 128-byte swizzle, this CTA only)
-//   warp 1      MMA issuer     one elected thread issues  S = Q K^T  (both operands in
-//                              shared memory) into one of two S buffers in tensor memory and
-//                              O += P V  (P read straight from tensor memory, V from shared
-//                              memory, N-major); completion is signalled with tcgen05.commit
-//   warps 2-5   softmax        thread r owns query row r: tcgen05.ld of the S row, scale,
-//                              bias, mask, running max / sum in the exp2 domain, dropout,
-//                              P written back over S as packed 16-bit, lazy rescale of O,
-//                              final normalisation, O and LSE stores
+//   warp 0       TMA producer   both Q tiles once, then K and V blocks through two 2-stage rings
+//                               (cp.async.bulk.tensor, 128-byte swizzle, this CTA only)
+//   warp 1       MMA issuer     one elected thread issues, per tile,  S = Q K^T  (operands in
+//                               shared memory) and  O += P V  (P read straight from tensor
+//                               memory, V from shared memory, N-major); completion is signalled
+//                               with tcgen05.commit
+//   warps 4-7    softmax, tile 0        thread r owns query row r of its tile: tcgen05.ld of the S
+//   warps 8-11   softmax, tile 1        row, scale, bias, mask, running max / sum in the exp2
+//                               domain, dropout, P written back over S as packed 16-bit, lazy
+//                               rescale of O, final normalisation, O and LSE stores
 //
-// Tensor memory (512 columns): S0 [0,128)  S1 [128,256)  O [256, 256+HD).  P_j aliases the
-// first 64 columns of S_{j%2}.  S_{j+1} is computed while the softmax warps work on S_j.
+// While one tile's softmax warps work on block j, the tensor core runs the other tile's PV and
+// QK^T: the two tiles ping-pong.  The producer and issuer warps give most of their registers
+// to the softmax warps (setmaxnreg).
+//
+// Tensor memory (512 columns): S0 [0,128)  S1 [128,256)  O0 [256,256+HD)  O1 [384,384+HD).
+// P of a tile aliases the first 64 columns of its S.
 //
 // Arithmetic contract (ROCm/aotriton modules/flash/kernel/fwd_kernel_inner.py:126-277,
 // fwd_kernel.py:573-620): logits scaled by sm_scale*log2(e), bias*log2(e) added, masked
@@ -33,36 +38,57 @@ namespace ab200 {
 
 __device__ unsigned int g_sm100_fwd_status = 0;
 
+// Optional pipeline trace (compile with -DAB200_TRACE): SM cycle stamps of one softmax thread
+// of the first CTA, eight per key block, read back with ab200_debug_read_fwd_trace().
+#ifndef AB200_TRACE_TID
+#define AB200_TRACE_TID 128
+#endif
+#ifdef AB200_TRACE
+__device__ long long g_fwd_trace[8 * 256];
+#define AB200_FSTAMP(iter, slot)                                                                                     \
+  do {                                                                                                               \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == AB200_TRACE_TID && (iter) < 256)     \
+      g_fwd_trace[(iter) * 8 + (slot)] = clock64();                                                                  \
+  } while (0)
+#else
+#define AB200_FSTAMP(iter, slot) do {} while (0)
+#endif
+
 namespace {
 
 using namespace ptx;
 
 constexpr int kBM = 128, kBN = 128, kStages = 2;
-constexpr int kFwdThreads = 192;
+constexpr int kCtaRows = 2 * kBM;
+constexpr int kFwdThreads = 384;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;
+// Strict alternation of the two tiles' softmax (tile 0 block j, tile 1 block j, ...).  Measured
+// slower than letting the warpgroups overlap freely (0.87 ms vs 0.70 ms on the benchmark), because
+// one softmax warp per scheduler cannot keep the FMA, ALU and special-function pipes busy at once.
+constexpr bool kTakeTurns = false;
 
 template <int HD>
 struct FwdSmem {
   static constexpr int kHalves = HD / 64;
   static constexpr int kTileBytes = kHalves * 128 * 128;     // 128 rows x HD x 2 bytes
-  static constexpr int kQ = 0;
-  static constexpr int kK = kQ + kTileBytes;
+  static constexpr int kQ = 0;                               // two tiles
+  static constexpr int kK = kQ + 2 * kTileBytes;
   static constexpr int kV = kK + kStages * kTileBytes;
   static constexpr int kBars = kV + kStages * kTileBytes;
   // barrier slots (8 bytes each)
-  static constexpr int bQFull = 0, bKFull = 1, bKEmpty = 3, bVFull = 5, bVEmpty = 7, bSFull = 9, bPFull = 11,
-                       bPvDone = 13, bCount = 14;
+  static constexpr int bQFull = 0 /*2*/, bKFull = 2, bKEmpty = 4, bVFull = 6, bVEmpty = 8, bSFull = 10 /*2*/,
+                       bPFull = 12 /*2*/, bPvDone = 14 /*2*/, bTurn = 16 /*2*/, bCount = 18;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4;
   static constexpr int kDynamic = kTotal + 1024;             // slack for manual 1024-byte alignment
 };
 
-// Rows of the tile that have no key at all: O = 0, LSE = +inf.
+// Rows [m0, m0+rows) of the output that have no key at all: O = 0, LSE = +inf.
 template <typename T>
-__device__ void write_dead_tile(const Params& p, const Seq& sq, int h, int m0) {
-  for (int r = threadIdx.x; r < kBM; r += blockDim.x) {
+__device__ void write_dead_rows(const Params& p, const Seq& sq, int h, int m0, int rows) {
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) {
     int m = m0 + r;
     if (m >= sq.sq) continue;
     T* op = reinterpret_cast<T*>(p.out.ptr) + (int64_t)sq.bidx * p.out.s[0] + (int64_t)h * p.out.s[1] +
@@ -86,7 +112,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int z = blockIdx.z, h = blockIdx.y;
-  const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * kBM;     // long tiles of a causal problem first
+  const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * kCtaRows;   // long tiles of a causal problem first
   if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;   // an earlier CTA timed out
   // One thread of the grid reports the seed and offset actually used, before any early exit.
   if (p.dropout_on && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
@@ -98,11 +124,13 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
   const Seq sq = resolve_seq(p, z);
   if (m0 >= sq.sq) return;
   const int hk = h / p.group;
+  const int ntile = (m0 + kBM < sq.sq) ? 2 : 1;                   // the second tile may lie beyond the sequence
 
+  // Block range: the union over the CTA's rows; a tile simply sees fully masked blocks outside its own.
   int n_lo, n_hi;
-  key_range(p, sq, m0, min(m0 + kBM, sq.sq) - 1, n_lo, n_hi);
+  key_range(p, sq, m0, min(m0 + kCtaRows, sq.sq) - 1, n_lo, n_hi);
   if (n_hi < n_lo) {            // CTA-uniform: nothing to attend to
-    write_dead_tile<T>(p, sq, h, m0);
+    write_dead_rows<T>(p, sq, h, m0, kCtaRows);
     return;
   }
   const int jb_lo = n_lo / kBN;
@@ -111,18 +139,17 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
   // ---- set-up -----------------------------------------------------------------------
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    mbar_init(&bars[L::bQFull], 1);
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars[L::bQFull + s], 1);
       mbar_init(&bars[L::bKFull + s], 1);
       mbar_init(&bars[L::bKEmpty + s], 1);
       mbar_init(&bars[L::bVFull + s], 1);
       mbar_init(&bars[L::bVEmpty + s], 1);
-    }
-    for (int s = 0; s < 2; ++s) {
       mbar_init(&bars[L::bSFull + s], 1);
-      mbar_init(&bars[L::bPFull + s], 4);      // one arrival per softmax warp
+      mbar_init(&bars[L::bPFull + s], 4);      // one arrival per softmax warp of the tile
+      mbar_init(&bars[L::bPvDone + s], 1);
+      mbar_init(&bars[L::bTurn + s], 4);       // passed on by the four warps of the other tile
     }
-    mbar_init(&bars[L::bPvDone], 1);
     fence_barrier_init();
     prefetch_tmap(&tm_q);
     prefetch_tmap(&tm_k);
@@ -136,99 +163,120 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;
 
-  if (warp == 0) {
-    // =============================== TMA producer ===================================
-    if (lane == 0) {
-      const int qrow = (int)(sq.q0 + m0);
-      mbar_expect_tx(&bars[L::bQFull], L::kTileBytes);
-      for (int hf = 0; hf < L::kHalves; ++hf)
-        tma_load_4d(smem + L::kQ + hf * 16384, &tm_q, &bars[L::bQFull], hf * 64, qrow, h, sq.bidx);
-      int issued = 0;
-      for (int j = 0; j < nblk; ++j) {
-        const int s = j % kStages;
-        const uint32_t ph = (uint32_t)(j / kStages) & 1u;
-        const int krow = (int)(sq.k0 + (int64_t)(jb_lo + j) * kBN);
-        if (!mbar_wait(&bars[L::bKEmpty + s], ph ^ 1u, abort_flag, status, 0x100 + j)) break;
-        mbar_expect_tx(&bars[L::bKFull + s], L::kTileBytes);
-        for (int hf = 0; hf < L::kHalves; ++hf)
-          tma_load_4d(smem + L::kK + s * L::kTileBytes + hf * 16384, &tm_k, &bars[L::bKFull + s], hf * 64, krow, hk,
-                      sq.bidx);
-        if (!mbar_wait(&bars[L::bVEmpty + s], ph ^ 1u, abort_flag, status, 0x200 + j)) { issued = j * 2 + 1; break; }
-        mbar_expect_tx(&bars[L::bVFull + s], L::kTileBytes);
-        for (int hf = 0; hf < L::kHalves; ++hf)
-          tma_load_4d(smem + L::kV + s * L::kTileBytes + hf * 16384, &tm_v, &bars[L::bVFull + s], hf * 64, krow, hk,
-                      sq.bidx);
-        issued = j * 2 + 2;
-      }
-      if (*abort_flag) {
-        // Let copies that are still in flight land before the CTA gives its shared memory back.
-        mbar_wait_quiet(&bars[L::bQFull], 0);
-        for (int i = max(0, issued - 2 * kStages); i < issued; ++i) {
-          int j = i >> 1, s = j % kStages;
-          uint32_t ph = (uint32_t)(j / kStages) & 1u;
-          mbar_wait_quiet((i & 1) ? &bars[L::bVFull + s] : &bars[L::bKFull + s], ph);
+  if (warp < 4) {
+    reg_dealloc<40>();
+    if (warp == 0) {
+      // =============================== TMA producer ===================================
+      if (lane == 0) {
+        for (int t = 0; t < ntile; ++t) {
+          const int qrow = (int)(sq.q0 + m0 + t * kBM);
+          mbar_expect_tx(&bars[L::bQFull + t], L::kTileBytes);
+          for (int hf = 0; hf < L::kHalves; ++hf)
+            tma_load_4d(smem + L::kQ + t * L::kTileBytes + hf * 16384, &tm_q, &bars[L::bQFull + t], hf * 64, qrow, h,
+                        sq.bidx);
+        }
+        int issued = 0;
+        for (int j = 0; j < nblk; ++j) {
+          const int s = j % kStages;
+          const uint32_t ph = (uint32_t)(j / kStages) & 1u;
+          const int krow = (int)(sq.k0 + (int64_t)(jb_lo + j) * kBN);
+          if (!mbar_wait(&bars[L::bKEmpty + s], ph ^ 1u, abort_flag, status, 0x100 + j)) break;
+          mbar_expect_tx(&bars[L::bKFull + s], L::kTileBytes);
+          for (int hf = 0; hf < L::kHalves; ++hf)
+            tma_load_4d(smem + L::kK + s * L::kTileBytes + hf * 16384, &tm_k, &bars[L::bKFull + s], hf * 64, krow, hk,
+                        sq.bidx);
+          if (!mbar_wait(&bars[L::bVEmpty + s], ph ^ 1u, abort_flag, status, 0x200 + j)) { issued = j * 2 + 1; break; }
+          mbar_expect_tx(&bars[L::bVFull + s], L::kTileBytes);
+          for (int hf = 0; hf < L::kHalves; ++hf)
+            tma_load_4d(smem + L::kV + s * L::kTileBytes + hf * 16384, &tm_v, &bars[L::bVFull + s], hf * 64, krow, hk,
+                        sq.bidx);
+          issued = j * 2 + 2;
+        }
+        if (*abort_flag) {
+          // Let copies that are still in flight land before the CTA gives its shared memory back.
+          for (int t = 0; t < ntile; ++t) mbar_wait_quiet(&bars[L::bQFull + t], 0);
+          for (int i = max(0, issued - 2 * kStages); i < issued; ++i) {
+            int j = i >> 1, s = j % kStages;
+            uint32_t ph = (uint32_t)(j / kStages) & 1u;
+            mbar_wait_quiet((i & 1) ? &bars[L::bVFull + s] : &bars[L::bKFull + s], ph);
+          }
         }
       }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ================================ MMA issuer ====================================
-    if (lane == 0) {
-      constexpr uint32_t kIdescQK = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
-      constexpr uint32_t kIdescPV = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
-      // Descriptors are built once; a k-step or a ring stage only moves the 14-bit start-address
-      // field (units of 16 bytes), which cannot carry out of the field for in-range addresses.
-      const uint64_t q_desc = smem_desc_sw128(smem_u32(smem + L::kQ), 16, 1024);
-      const uint64_t k_desc = smem_desc_sw128(smem_u32(smem + L::kK), 16, 1024);
-      const uint64_t v_desc = smem_desc_sw128(smem_u32(smem + L::kV), 16384, 1024);
-      constexpr uint32_t kStageStep = L::kTileBytes >> 4;
-      bool ok = mbar_wait(&bars[L::bQFull], 0, abort_flag, status, 0x300);
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j % kStages;
-        if (!mbar_wait(&bars[L::bKFull + s], (uint32_t)(j / kStages) & 1u, abort_flag, status, 0x400 + j)) return false;
-        tc_fence_after();
-        const uint32_t d = tmem_base + (uint32_t)(j & 1) * 128u;
-        const uint64_t kd = k_desc + (uint64_t)((uint32_t)s * kStageStep);
+      __syncwarp();
+    } else if (warp == 1) {
+      // ================================ MMA issuer ====================================
+      if (lane == 0) {
+        constexpr uint32_t kIdescQK = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
+        constexpr uint32_t kIdescPV = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
+        // Descriptors are built once; a k-step, a tile or a ring stage only moves the 14-bit
+        // start-address field (units of 16 bytes), which cannot carry out of the field.
+        const uint64_t q_desc = smem_desc_sw128(smem_u32(smem + L::kQ), 16, 1024);
+        const uint64_t k_desc = smem_desc_sw128(smem_u32(smem + L::kK), 16, 1024);
+        const uint64_t v_desc = smem_desc_sw128(smem_u32(smem + L::kV), 16384, 1024);
+        constexpr uint32_t kStageStep = L::kTileBytes >> 4;
+        auto issue_qk = [&](int t, int j) {       // S_t = Q_t K_j^T
+          const uint64_t qd = q_desc + (uint64_t)((uint32_t)t * kStageStep);
+          const uint64_t kd = k_desc + (uint64_t)((uint32_t)(j % kStages) * kStageStep);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          constexpr uint32_t kHalfStep = 16384u >> 4, kInner = 32u >> 4;
-          const uint32_t off = (uint32_t)(kk >> 2) * kHalfStep + (uint32_t)(kk & 3) * kInner;
-          mma_ss(d, q_desc + off, kd + off, kIdescQK, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            constexpr uint32_t kHalfStep = 16384u >> 4, kInner = 32u >> 4;
+            const uint32_t off = (uint32_t)(kk >> 2) * kHalfStep + (uint32_t)(kk & 3) * kInner;
+            mma_ss(tmem_base + (uint32_t)t * 128u, qd + off, kd + off, kIdescQK, kk > 0 ? 1u : 0u);
+          }
+          mma_commit(&bars[L::bSFull + t]);
+        };
+        bool ok = true;
+        for (int t = 0; ok && t < ntile; ++t) ok = mbar_wait(&bars[L::bQFull + t], 0, abort_flag, status, 0x300 + t);
+        if (ok) ok = mbar_wait(&bars[L::bKFull + 0], 0, abort_flag, status, 0x400);
+        if (ok) {
+          tc_fence_after();
+          for (int t = 0; t < ntile; ++t) issue_qk(t, 0);
+          mma_commit(&bars[L::bKEmpty + 0]);
         }
-        mma_commit(&bars[L::bKEmpty + s]);
-        mma_commit(&bars[L::bSFull + (j & 1)]);
-        return true;
-      };
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; ok && j < nblk; ++j) {
-        if (j + 1 < nblk) {
-          if (!issue_qk(j + 1)) break;
-        }
-        const int s = j % kStages;
-        if (!mbar_wait(&bars[L::bPFull + (j & 1)], (uint32_t)(j >> 1) & 1u, abort_flag, status, 0x500 + j)) break;
-        if (!mbar_wait(&bars[L::bVFull + s], (uint32_t)(j / kStages) & 1u, abort_flag, status, 0x600 + j)) break;
-        tc_fence_after();
-        const uint32_t pcol = tmem_base + (uint32_t)(j & 1) * 128u;
-        const uint64_t vd = v_desc + (uint64_t)((uint32_t)s * kStageStep);
-        const uint32_t first = (j > 0) ? 1u : 0u;
+        for (int j = 0; ok && j < nblk; ++j) {
+          const int s = j % kStages;
+          const uint32_t par = (uint32_t)j & 1u;
+          if (!mbar_wait(&bars[L::bVFull + s], (uint32_t)(j / kStages) & 1u, abort_flag, status, 0x600 + j)) break;
+          if (j + 1 < nblk) {
+            if (!mbar_wait(&bars[L::bKFull + ((j + 1) % kStages)], (uint32_t)((j + 1) / kStages) & 1u, abort_flag,
+                           status, 0x400 + j + 1))
+              break;
+          }
+          const uint64_t vd = v_desc + (uint64_t)((uint32_t)s * kStageStep);
+          const uint32_t first = (j > 0) ? 1u : 0u;
+          for (int t = 0; ok && t < ntile; ++t) {
+            if (!mbar_wait(&bars[L::bPFull + t], par, abort_flag, status, 0x500 + 2 * j + t)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t pcol = tmem_base + (uint32_t)t * 128u;
+            const uint32_t ocol = tmem_base + 256u + (uint32_t)t * 128u;
 #pragma unroll
-        for (int kk = 0; kk < kBN / 16; ++kk) {
-          // 16 keys per step: 8 packed columns of P, 2048 bytes of V (two 8-key groups)
-          mma_ts(tmem_o, pcol + (uint32_t)kk * 8u, vd + (uint32_t)kk * (2048u >> 4), kIdescPV, kk > 0 ? 1u : first);
+            for (int kk = 0; kk < kBN / 16; ++kk) {
+              // 16 keys per step: 8 packed columns of P, 2048 bytes of V (two 8-key groups)
+              mma_ts(ocol, pcol + (uint32_t)kk * 8u, vd + (uint32_t)kk * (2048u >> 4), kIdescPV, kk > 0 ? 1u : first);
+            }
+            mma_commit(&bars[L::bPvDone + t]);
+            if (t == ntile - 1) mma_commit(&bars[L::bVEmpty + s]);
+            if (j + 1 < nblk) {
+              issue_qk(t, j + 1);     // the tile's S buffer is free again: PV_t(j), just issued, runs first
+              if (t == ntile - 1) mma_commit(&bars[L::bKEmpty + ((j + 1) % kStages)]);
+            }
+          }
         }
-        mma_commit(&bars[L::bVEmpty + s]);
-        mma_commit(&bars[L::bPvDone]);
       }
+      __syncwarp();
     }
-    __syncwarp();
   } else {
     // ================================== softmax =====================================
+    reg_alloc<224>();
+    const int t = (warp - 4) >> 2;              // tile of this warpgroup
+    if (t < ntile) {
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    const int m = m0 + r;
+    const int m = m0 + t * kBM + r;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)t * 128u;
+    const uint32_t o_addr = tmem_base + lane_addr + 256u + (uint32_t)t * 128u;
     int row_lo = 0, row_hi = sq.sk - 1;
     if (p.causal) {
       int64_t lo = (int64_t)m - sq.wl, hi = (int64_t)m + sq.wr;
@@ -247,14 +295,21 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
     bool ok = true;
     for (int j = 0; j < nblk; ++j) {
       const int n0 = (jb_lo + j) * kBN;
-      const int sb = j & 1;
-      if (!mbar_wait(&bars[L::bSFull + sb], (uint32_t)(j >> 1) & 1u, abort_flag, status, 0x700 + j)) { ok = false; break; }
+      const uint32_t par = (uint32_t)j & 1u;
+      if (!mbar_wait(&bars[L::bSFull + t], par, abort_flag, status, 0x700 + 2 * j + t)) { ok = false; break; }
+      // Optional strict ping-pong between the two tiles (see kTakeTurns).
+      if (kTakeTurns && ntile == 2 &&
+          !mbar_wait(&bars[L::bTurn + t], t == 0 ? (par ^ 1u) : par, abort_flag, status, 0xA00 + 2 * j + t)) {
+        ok = false;
+        break;
+      }
+      AB200_FSTAMP(j, 0);
       tc_fence_after();
       float sc[128];
-      const uint32_t s_addr = tmem_base + lane_addr + (uint32_t)sb * 128u;
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32f(s_addr + c * 32, &sc[c * 32]);
       tmem_wait_ld();
+      AB200_FSTAMP(j, 1);
       // Scores -> exponent arguments.  The common case (no bias, positive scale, ordinary
       // magnitudes) keeps the raw scores and folds scale and maximum into one FMA per element
       // later.  Otherwise the scaled scores are formed first, so that equal raw scores give
@@ -304,6 +359,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         for (int c = 16; c < 128; c += 2) m8[(c >> 1) & 7] = fmax3(m8[(c >> 1) & 7], sc[c], sc[c + 1]);
         mx = fmaxf(fmax3(m8[0], m8[1], m8[2]), fmaxf(fmax3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7])));
       }
+      AB200_FSTAMP(j, 2);
       // Advance the reference maximum only when it moved by more than the threshold.
       const bool grow = mx > m_used + kRescaleThreshold;     // false when mx == -inf
       float alpha = 1.f;
@@ -313,19 +369,21 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       }
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
         // O must be complete up to block j-1 before it is rescaled.
-        if (!mbar_wait(&bars[L::bPvDone], (uint32_t)(j - 1) & 1u, abort_flag, status, 0x800 + j)) { ok = false; break; }
+        // (S of block j was issued behind P V of block j-1, so this wait returns at once.)
+        if (!mbar_wait(&bars[L::bPvDone + t], (uint32_t)(j - 1) & 1u, abort_flag, status, 0x800 + 2 * j + t)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t o[32];
-          tmem_ld32(tmem_o + lane_addr + c * 32, o);
+          tmem_ld32(o_addr + c * 32, o);
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tmem_o + lane_addr + c * 32, o);
+          tmem_st32(o_addr + c * 32, o);
         }
         tmem_wait_st();
       }
+      AB200_FSTAMP(j, 3);
       l *= alpha;
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
       float2 s4[4];
@@ -352,6 +410,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       }
       const float sum = ((s4[0].x + s4[0].y) + (s4[1].x + s4[1].y)) + ((s4[2].x + s4[2].y) + (s4[3].x + s4[3].y));
       l += sum;
+      AB200_FSTAMP(j, 4);
       if (p.dropout_on) {
         const int mm = min(m, p.max_sq - 1);
 #pragma unroll
@@ -370,17 +429,20 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(sc[c * 32 + 2 * i], sc[c * 32 + 2 * i + 1]);
         tmem_st16(s_addr + c * 16, pk);
       }
+      AB200_FSTAMP(j, 5);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[L::bPFull + sb]);
+      if (lane == 0) {
+        mbar_arrive(&bars[L::bPFull + t]);
+        if (kTakeTurns && ntile == 2) mbar_arrive(&bars[L::bTurn + (t ^ 1)]);
+      }
+      AB200_FSTAMP(j, 6);
     }
     // ---- epilogue ---------------------------------------------------------------------
-    // Holding S of the last block only guarantees that P V of all blocks but the last two has
-    // completed, and a parity wait can tell apart just two consecutive phases: wait for the
-    // last-but-one phase first, then for the last.
-    if (ok && nblk >= 2) ok = mbar_wait(&bars[L::bPvDone], (uint32_t)(nblk - 2) & 1u, abort_flag, status, 0x8FF);
-    if (ok) ok = mbar_wait(&bars[L::bPvDone], (uint32_t)(nblk - 1) & 1u, abort_flag, status, 0x900);
+    // P V of every block but the last is complete (S of the last block was issued behind it),
+    // so only the last phase of this barrier can still be pending.
+    if (ok) ok = mbar_wait(&bars[L::bPvDone + t], (uint32_t)(nblk - 1) & 1u, abort_flag, status, 0x900 + t);
     if (ok) {
       tc_fence_after();
       const float inv = (l > 0.f) ? p.dropout_scale / l : 0.f;
@@ -389,7 +451,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t o[32];
-        tmem_ld32(tmem_o + lane_addr + c * 32, o);
+        tmem_ld32(o_addr + c * 32, o);
         tmem_wait_ld();
         if (m < sq.sq) {
 #pragma unroll
@@ -410,6 +472,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       if (p.lse != nullptr && m < sq.sq)
         p.lse[lse_offset(p, sq, h) + m] = (l > 0.f) ? (m_used + log2f(l)) * kLn2 : INFINITY;
     }
+    }   // t < ntile
   }
 
   // ---- tear-down ------------------------------------------------------------------------
@@ -436,7 +499,7 @@ cudaError_t launch_fwd_T(const Params& p, cudaStream_t st) {
   unsigned int* status = nullptr;
   e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_sm100_fwd_status);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.max_sq + kBM - 1) / kBM, p.hq, p.batch);
+  dim3 grid((p.max_sq + kCtaRows - 1) / kCtaRows, p.hq, p.batch);
   sm100_fwd_kernel<T, HD><<<grid, kFwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, status);
   count_launch();
   return cudaGetLastError();
@@ -460,6 +523,12 @@ cudaError_t launch_sm100_fwd(int dtype, const Params& p, cudaStream_t st) {
   if (dtype == 2) return small ? launch_fwd_T<__half, 64>(p, st) : launch_fwd_T<__half, 128>(p, st);
   return small ? launch_fwd_T<__nv_bfloat16, 64>(p, st) : launch_fwd_T<__nv_bfloat16, 128>(p, st);
 }
+
+#ifdef AB200_TRACE
+extern "C" __attribute__((visibility("default"))) int ab200_debug_read_fwd_trace(long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, g_fwd_trace, sizeof(long long) * (size_t)(n < 2048 ? n : 2048));
+}
+#endif
 
 unsigned int sm100_fwd_status(bool reset) {
   unsigned int v = 0;
