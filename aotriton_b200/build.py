@@ -48,6 +48,8 @@ def _suffix_flags() -> list[str]:
         flags.append("-DAB200_TRACE")
         if os.environ.get("AB200_TRACE_TID"):
             flags.append("-DAB200_TRACE_TID=" + os.environ["AB200_TRACE_TID"])
+    if os.environ.get("AB200_EXTRA_DEFS"):     # experiments: space-separated -D definitions
+        flags += os.environ["AB200_EXTRA_DEFS"].split()
     return flags
 
 

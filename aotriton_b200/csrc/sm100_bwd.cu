@@ -55,6 +55,14 @@ __device__ long long g_bwd_trace[16 * 256];
 #else
 #define AB200_STAMP(iter, slot) do {} while (0)
 #endif
+#if defined(AB200_TRACE) && defined(AB200_TRACE_DQ)   // stamps of the dQ kernel's last-launched first CTA instead
+#define AB200_STAMPQ(iter, slot)                                                                        \
+  do {                                                                                                  \
+    if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0 && (iter) < 256) g_bwd_trace[(iter) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define AB200_STAMPQ(iter, slot) do {} while (0)
+#endif
 
 namespace {
 
@@ -77,7 +85,9 @@ struct BwdSmem {
   static constexpr int kAuxFlag = kAux + 2 * 256 * 4;    // per stage: 1 when some |lse2| is huge
   static constexpr int kBars = kAuxFlag + 16;
   static constexpr int bResFull = 0, bRingFull = 1, bRingEmpty = 3, bAuxFull = 5, bAuxEmpty = 7, bSFull = 9,
-                       bDpFull = 10 /* two: one per dP buffer in the dQ kernel */, bDsFull = 12, bAccDone = 13, bSRead = 14, bCount = 15;
+                       bDpFull = 10 /* two: one per dP buffer in the dQ kernel */, bDsFull = 12, bAccDone = 13, bSRead = 14,
+                       bResEmpty = 15, bVFull = 16 /* dQ kernel: V has a ring of its own */, bVEmpty = 18,
+                       bDsFull2 = 20 /* dQ kernel: one per dP buffer */, bCount = 22;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kDynamic = kAbort + 4 + 1024;
@@ -132,6 +142,9 @@ __device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t*
     mbar_init(&bars[L::bRingEmpty + s], 1);
     mbar_init(&bars[L::bAuxFull + s], 1);
     mbar_init(&bars[L::bAuxEmpty + s], kComputeWarps);
+    mbar_init(&bars[L::bVFull + s], 1);
+    mbar_init(&bars[L::bVEmpty + s], 1);
+    mbar_init(&bars[L::bDsFull2 + s], kComputeWarps);
   }
   mbar_init(&bars[L::bSFull], 1);
   mbar_init(&bars[L::bDpFull], 1);
@@ -139,16 +152,53 @@ __device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t*
   mbar_init(&bars[L::bDsFull], kComputeWarps);
   mbar_init(&bars[L::bAccDone], 1);
   mbar_init(&bars[L::bSRead], kComputeWarps);
+  mbar_init(&bars[L::bResEmpty], 1);
   fence_barrier_init();
 }
 
 // =========================================================================================
-// dK / dV.  grid = (cdiv(max_sk, 128), Hk, batch)
+// dK / dV.  Persistent: one CTA per SM walks work items (128 keys of one sequence and kv head),
+// heaviest first; the pipeline (rings, barriers, tensor memory) stays up across items, so the
+// next item's K/V and first Q/dO blocks are fetched and its first two GEMMs issued while the
+// current item is still finishing.  All roles enumerate the same items and keep the same running
+// counters: G counts query-block iterations since the kernel started (ring stage G&1, hand-off
+// parity G&1), `live` counts items that had work (parity of the once-per-item barriers).
+struct DkdvItem {
+  int z, hk, n0;
+  Seq sq;
+  int mb_lo, nmb, niter;   // niter == 0: keys no query attends to (gradients are zero)
+  bool valid;              // false: key block beyond this sequence
+};
+
+__device__ __forceinline__ DkdvItem dkdv_item(const Params& p, int w) {
+  DkdvItem it;
+  const int per = p.batch * p.hk;
+  const int nkb = (p.max_sk + kBlk - 1) / kBlk;
+  const int grp = w / (nkb * 8), r = w - grp * (nkb * 8);
+  const int kb = r >> 3, rem = grp * 8 + (r & 7);
+  it.z = min(rem, per - 1) / p.hk;
+  it.hk = min(rem, per - 1) - it.z * p.hk;
+  it.n0 = kb * kBlk;
+  it.sq = resolve_seq(p, it.z);
+  it.valid = rem < per && it.n0 < it.sq.sk;
+  it.mb_lo = it.nmb = it.niter = 0;
+  if (it.valid) {
+    int m_lo, m_hi;
+    query_range(p, it.sq, it.n0, min(it.n0 + kBlk, it.sq.sk) - 1, m_lo, m_hi);
+    if (m_hi >= m_lo) {
+      it.mb_lo = m_lo / kBlk;
+      it.nmb = m_hi / kBlk - it.mb_lo + 1;
+      it.niter = it.nmb * p.group;
+    }
+  }
+  return it;
+}
+
 template <typename T, int HD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                      const __grid_constant__ CUtensorMap tm_do, unsigned int* status) {
+                      const __grid_constant__ CUtensorMap tm_do, unsigned int* status, int nitems) {
   using L = BwdSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -159,20 +209,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
   volatile uint32_t* aux_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAuxFlag);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int z = blockIdx.z, hk = blockIdx.y, n0 = blockIdx.x * kBlk;
   if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
-  const Seq sq = resolve_seq(p, z);
-  if (n0 >= sq.sk) return;
-  int m_lo, m_hi;
-  query_range(p, sq, n0, min(n0 + kBlk, sq.sk) - 1, m_lo, m_hi);
-  if (m_hi < m_lo) {   // no query attends to these keys
-    zero_rows<T>(p.dk, sq.bidx, hk, sq.k0, n0, sq.sk, p.dqk);
-    zero_rows<T>(p.dv, sq.bidx, hk, sq.k0, n0, sq.sk, p.dvo);
-    return;
-  }
-  const int mb_lo = m_lo / kBlk;
-  const int nmb = m_hi / kBlk - mb_lo + 1;
-  const int niter = nmb * p.group;
 
   if (threadIdx.x == 0) {
     init_barriers<HD>(bars, abort_flag);
@@ -188,36 +225,45 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
+    // ================================ TMA producer ===================================
     if (lane == 0) {
-      const int krow = (int)(sq.k0 + n0);
-      mbar_expect_tx(&bars[L::bResFull], 2 * L::kTile);
-      for (int hf = 0; hf < L::kHalves; ++hf) {
-        tma_load_4d(smem + L::kResA + hf * 16384, &tm_k, &bars[L::bResFull], hf * 64, krow, hk, sq.bidx);
-        tma_load_4d(smem + L::kResB + hf * 16384, &tm_v, &bars[L::bResFull], hf * 64, krow, hk, sq.bidx);
-      }
-      int issued = 0;
-      for (int i = 0; i < niter; ++i) {
-        const int s = i & 1;
-        const uint32_t ph = (uint32_t)(i >> 1) & 1u;
-        const int h = hk * p.group + i / nmb;
-        const int mrow = (int)(sq.q0 + (int64_t)(mb_lo + i % nmb) * kBlk);
-        if (!mbar_wait(&bars[L::bRingEmpty + s], ph ^ 1u, abort_flag, status, 0x1100 + i)) break;
-        mbar_expect_tx(&bars[L::bRingFull + s], 2 * L::kTile);
+      uint32_t G = 0, live = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < nitems; w += gridDim.x) {
+        const DkdvItem it = dkdv_item(p, w);
+        if (!it.valid || it.niter == 0) continue;
+        // K and V of the previous item are free once its last S and dP GEMMs have run.
+        if (!mbar_wait(&bars[L::bResEmpty], (live & 1u) ^ 1u, abort_flag, status, 0x1000)) break;
+        const int krow = (int)(it.sq.k0 + it.n0);
+        mbar_expect_tx(&bars[L::bResFull], 2 * L::kTile);
         for (int hf = 0; hf < L::kHalves; ++hf) {
-          tma_load_4d(smem + L::kRingA + s * L::kTile + hf * 16384, &tm_q, &bars[L::bRingFull + s], hf * 64, mrow, h,
-                      sq.bidx);
-          tma_load_4d(smem + L::kRingB + s * L::kTile + hf * 16384, &tm_do, &bars[L::bRingFull + s], hf * 64, mrow, h,
-                      sq.bidx);
+          tma_load_4d(smem + L::kResA + hf * 16384, &tm_k, &bars[L::bResFull], hf * 64, krow, it.hk, it.sq.bidx);
+          tma_load_4d(smem + L::kResB + hf * 16384, &tm_v, &bars[L::bResFull], hf * 64, krow, it.hk, it.sq.bidx);
         }
-        issued = i + 1;
+        for (int i = 0; i < it.niter; ++i, ++G) {
+          const int s = (int)(G & 1u);
+          const int h = it.hk * p.group + i / it.nmb;
+          const int mrow = (int)(it.sq.q0 + (int64_t)(it.mb_lo + i % it.nmb) * kBlk);
+          if (!mbar_wait(&bars[L::bRingEmpty + s], ((G >> 1) & 1u) ^ 1u, abort_flag, status, 0x1100)) { ok = false; break; }
+          mbar_expect_tx(&bars[L::bRingFull + s], 2 * L::kTile);
+          for (int hf = 0; hf < L::kHalves; ++hf) {
+            tma_load_4d(smem + L::kRingA + s * L::kTile + hf * 16384, &tm_q, &bars[L::bRingFull + s], hf * 64, mrow, h,
+                        it.sq.bidx);
+            tma_load_4d(smem + L::kRingB + s * L::kTile + hf * 16384, &tm_do, &bars[L::bRingFull + s], hf * 64, mrow, h,
+                        it.sq.bidx);
+          }
+        }
+        ++live;
       }
       if (*abort_flag) {
-        mbar_wait_quiet(&bars[L::bResFull], 0);
-        for (int i = max(0, issued - 2); i < issued; ++i) mbar_wait_quiet(&bars[L::bRingFull + (i & 1)], (uint32_t)(i >> 1) & 1u);
+        // Let copies that are still in flight land before the CTA gives its shared memory back.
+        if (live > 0) mbar_wait_quiet(&bars[L::bResFull], (live - 1) & 1u);
+        for (uint32_t g = (G >= 2 ? G - 2 : 0); g < G; ++g) mbar_wait_quiet(&bars[L::bRingFull + (g & 1u)], (g >> 1) & 1u);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
+    // ================================= MMA issuer ====================================
     if (lane == 0) {
       constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
       constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
@@ -225,241 +271,300 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       const uint64_t k_km = kmajor_base(smem_u32(smem + L::kResA)), v_km = kmajor_base(smem_u32(smem + L::kResB));
       const uint64_t q_km = kmajor_base(smem_u32(smem + L::kRingA)), do_km = kmajor_base(smem_u32(smem + L::kRingB));
       const uint64_t q_mn = mnmajor_base(smem_u32(smem + L::kRingA)), do_mn = mnmajor_base(smem_u32(smem + L::kRingB));
-      auto issue_s = [&](int i) {      // S^T = K Q_i^T
-        const uint64_t qa = q_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
+      auto issue_s = [&](uint32_t g) {      // S^T = K Q_g^T
+        const uint64_t qa = q_km + (uint64_t)((g & 1u) * kStageStep);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
+        for (int kk = 0; kk < HD / 16; ++kk) {
           mma_ss(tmem_base + kColS, k_km + kmajor_step(kk), qa + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
+          if (kk == 0) AB200_STAMP(g & 255u, 13);
+          if (kk == 3) AB200_STAMP(g & 255u, 12);
+        }
+        AB200_STAMP(g & 255u, 15);
         mma_commit(&bars[L::bSFull]);
       };
-      auto issue_dp = [&](int i) {     // dP^T = V dO_i^T
-        const uint64_t da = do_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
+      auto issue_dp = [&](uint32_t g) {     // dP^T = V dO_g^T
+        const uint64_t da = do_km + (uint64_t)((g & 1u) * kStageStep);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
           mma_ss(tmem_base + kColDP, v_km + kmajor_step(kk), da + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
         mma_commit(&bars[L::bDpFull]);
       };
-      bool ok = mbar_wait(&bars[L::bResFull], 0, abort_flag, status, 0x1200) &&
-                mbar_wait(&bars[L::bRingFull + 0], 0, abort_flag, status, 0x1201);
-      if (ok) {
+      uint32_t G = 0, live = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < nitems; w += gridDim.x) {
+        const DkdvItem it = dkdv_item(p, w);
+        if (!it.valid || it.niter == 0) continue;
+        // first iteration of the item: K/V resident, Q/dO block landed, S buffer read out by the
+        // compute warps (the dP buffer is released in issue order by the previous item's dV/dK)
+        if (!mbar_wait(&bars[L::bResFull], live & 1u, abort_flag, status, 0x1200)) break;
+        if (G > 0 && !mbar_wait(&bars[L::bSRead], (G - 1) & 1u, abort_flag, status, 0x1201)) break;
+        if (!mbar_wait(&bars[L::bRingFull + (G & 1u)], (G >> 1) & 1u, abort_flag, status, 0x1202)) break;
         tc_fence_after();
-        issue_s(0);
-        issue_dp(0);
-      }
-      for (int i = 0; ok && i < niter; ++i) {
-        const int s = i & 1;
-        const uint32_t par = (uint32_t)i & 1u;
-        if (i + 1 < niter) {
-          // S_i sits in registers of every compute thread: its buffer can take S_{i+1} already.
-          if (!mbar_wait(&bars[L::bSRead], par, abort_flag, status, 0x1300 + i)) break;
-          if (!mbar_wait(&bars[L::bRingFull + ((i + 1) & 1)], (uint32_t)((i + 1) >> 1) & 1u, abort_flag, status,
-                         0x1400 + i))
-            break;
+        issue_s(G);
+        issue_dp(G);
+        if (it.niter == 1) mma_commit(&bars[L::bResEmpty]);
+        for (int i = 0; i < it.niter; ++i, ++G) {
+          const uint32_t s = G & 1u, par = G & 1u;
+          if (i + 1 < it.niter) {
+            // S_g sits in registers of every compute thread: its buffer can take S_{g+1} already.
+            if (!mbar_wait(&bars[L::bSRead], par, abort_flag, status, 0x1300)) { ok = false; break; }
+            if (!mbar_wait(&bars[L::bRingFull + ((G + 1) & 1u)], ((G + 1) >> 1) & 1u, abort_flag, status, 0x1400)) {
+              ok = false;
+              break;
+            }
+            AB200_STAMP(i + 1, 14);
+            tc_fence_after();
+            issue_s(G + 1);
+            AB200_STAMP(i + 1, 8);
+          }
+          if (!mbar_wait(&bars[L::bDsFull], par, abort_flag, status, 0x1500)) { ok = false; break; }
+          AB200_STAMP(i, 5);
           tc_fence_after();
-          issue_s(i + 1);
-        }
-        if (!mbar_wait(&bars[L::bDsFull], par, abort_flag, status, 0x1500 + i)) break;
-        AB200_STAMP(i, 5);
-        tc_fence_after();
-        const uint32_t first = (i > 0) ? 1u : 0u;
-        {   // dV += P^T dO_i   (P^T: first 16 packed columns of each warpgroup's range of the dP buffer)
-          const uint64_t da = do_mn + (uint64_t)((uint32_t)s * kStageStep);
+          const uint32_t first = (i > 0) ? 1u : 0u;
+          {   // dV += P^T dO_g   (P^T: first 16 packed columns of each warpgroup's range of the dP buffer)
+            const uint64_t da = do_mn + (uint64_t)(s * kStageStep);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tmem_base + kColAcc0, tmem_base + kColDP + split_a_col(kk), da + mnmajor_step(kk), kIdescTS,
-                   kk > 0 ? 1u : first);
-        }
-        {   // dK += dS^T Q_i  (dS^T: the next 16 packed columns)
-          const uint64_t qa = q_mn + (uint64_t)((uint32_t)s * kStageStep);
+            for (int kk = 0; kk < 8; ++kk)
+              mma_ts(tmem_base + kColAcc0, tmem_base + kColDP + split_a_col(kk), da + mnmajor_step(kk), kIdescTS,
+                     kk > 0 ? 1u : first);
+          }
+          {   // dK += dS^T Q_g  (dS^T: the next 16 packed columns)
+            const uint64_t qa = q_mn + (uint64_t)(s * kStageStep);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + 16u + split_a_col(kk), qa + mnmajor_step(kk), kIdescTS,
-                   kk > 0 ? 1u : first);
+            for (int kk = 0; kk < 8; ++kk)
+              mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + 16u + split_a_col(kk), qa + mnmajor_step(kk), kIdescTS,
+                     kk > 0 ? 1u : first);
+          }
+          mma_commit(&bars[L::bRingEmpty + s]);
+          if (i + 1 < it.niter) {
+            issue_dp(G + 1);
+            AB200_STAMP(i + 1, 9);
+            if (i + 2 == it.niter) mma_commit(&bars[L::bResEmpty]);   // last users of this item's K and V
+          }
         }
-        mma_commit(&bars[L::bRingEmpty + s]);
-        if (i + 1 < niter) issue_dp(i + 1);
+        if (!ok) break;
+        mma_commit(&bars[L::bAccDone]);
+        ++live;
       }
-      mma_commit(&bars[L::bAccDone]);
     }
     __syncwarp();
   } else if (warp == 2) {
-    // logsumexp (in log2 units) and delta of the streamed query block
-    for (int i = 0; i < niter; ++i) {
-      const int s = i & 1;
-      if (!mbar_wait(&bars[L::bAuxEmpty + s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag, status, 0x1600 + i)) break;
-      const int h = hk * p.group + i / nmb;
-      const int mbase = (mb_lo + i % nmb) * kBlk;
-      const int64_t lrow = lse_offset(p, sq, h);
-      float* dst = aux + s * 256;
-      bool huge = false;
+    // logsumexp (in log2 units) and delta of the streamed query blocks
+    uint32_t G = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; ok && w < nitems; w += gridDim.x) {
+      const DkdvItem it = dkdv_item(p, w);
+      if (!it.valid || it.niter == 0) continue;
+      for (int i = 0; i < it.niter; ++i, ++G) {
+        const int s = (int)(G & 1u);
+        if (!mbar_wait(&bars[L::bAuxEmpty + s], ((G >> 1) & 1u) ^ 1u, abort_flag, status, 0x1600)) { ok = false; break; }
+        const int h = it.hk * p.group + i / it.nmb;
+        const int mbase = (it.mb_lo + i % it.nmb) * kBlk;
+        const int64_t lrow = lse_offset(p, it.sq, h);
+        float* dst = aux + s * 256;
+        bool huge = false;
+        float l2[4], dl[4];
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const int c = lane * 4 + t, m = mbase + c;
-        const bool in = m < sq.sq;
-        const float l2 = in ? p.lse[lrow + m] * kLog2e : INFINITY;
-        dst[c] = l2;
-        dst[128 + c] = in ? p.delta[lrow + m] : 0.f;
-        huge = huge || (fabsf(l2) > 1.0e6f && l2 != INFINITY);
+        for (int t = 0; t < 4; ++t) {     // all eight loads in flight before the first store
+          const int m = mbase + lane * 4 + t;
+          const bool in = m < it.sq.sq;
+          l2[t] = in ? __ldg(p.lse + lrow + m) : INFINITY;
+          dl[t] = in ? __ldg(p.delta + lrow + m) : 0.f;
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          l2[t] *= kLog2e;
+          huge = huge || (fabsf(l2[t]) > 1.0e6f && l2[t] != INFINITY);
+        }
+        *reinterpret_cast<float4*>(dst + lane * 4) = make_float4(l2[0], l2[1], l2[2], l2[3]);
+        *reinterpret_cast<float4*>(dst + 128 + lane * 4) = make_float4(dl[0], dl[1], dl[2], dl[3]);
+        const bool any_huge = __any_sync(0xffffffffu, huge);
+        if (lane == 0) aux_flag[s] = any_huge ? 1u : 0u;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[L::bAuxFull + s]);
       }
-      const bool any_huge = __any_sync(0xffffffffu, huge);
-      if (lane == 0) aux_flag[s] = any_huge ? 1u : 0u;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[L::bAuxFull + s]);
     }
   } else if (warp >= 4) {
+    // ================================== compute ======================================
     const int quarter = warp & 3, wg = (warp - 4) >> 2;
     const int r = quarter * 32 + lane;
-    const int n = n0 + r;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int cbase = kWgCols * wg;
-    int col_lo = 0, col_hi = sq.sq - 1;     // valid query rows for this key
-    if (p.causal) {
-      int64_t lo = (int64_t)n - sq.wr, hi = (int64_t)n + sq.wl;
-      if (lo > col_lo) col_lo = (int)(lo > 0x7fffffffLL ? 0x7fffffffLL : lo);
-      if (hi < col_hi) col_hi = (int)(hi < -1 ? -1 : hi);
-    }
-    if (n >= sq.sk) { col_lo = 1; col_hi = 0; }
+    uint32_t G = 0, live = 0;
     bool ok = true;
-    for (int i = 0; i < niter; ++i) {
-      const int s = i & 1;
-      const uint32_t par = (uint32_t)i & 1u;
-      const int h = hk * p.group + i / nmb;
-      const int mbase = (mb_lo + i % nmb) * kBlk + cbase;    // first query row of this thread's columns
-      const float* lse2 = aux + s * 256 + cbase;
-      const float* dlt = lse2 + 128;
-      if (!mbar_wait(&bars[L::bAuxFull + s], (uint32_t)(i >> 1) & 1u, abort_flag, status, 0x1700 + i)) { ok = false; break; }
-      if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x1800 + i)) { ok = false; break; }
-      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 0);
-      tc_fence_after();
-      float pr[32];
-      tmem_ld32f(tmem_base + lane_addr + kColS + cbase, pr);
-      tmem_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[L::bSRead]);
-      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 6);
-      const bool need_mask = !(mbase >= col_lo && mbase + kWgCols - 1 <= col_hi);
-      const bool any_mask = __any_sync(0xffffffffu, need_mask);
-      // exponent arguments: scaled score (+ bias) minus the row's logsumexp, all in log2 units.
-      // Common case: one packed FMA per two elements.  With bias, or when the logsumexp is so
-      // large that product rounding matters (the aux warp flags that), scale first and subtract
-      // second, so that the forward's reference point cancels exactly.
-      if (!p.has_bias && aux_flag[s] == 0) {
-        const float2 sc2 = make_float2(p.qk_scale, p.qk_scale);
-#pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
-          const float2 a = fma2(make_float2(pr[4 * c4], pr[4 * c4 + 1]), sc2, make_float2(-l4.x, -l4.y));
-          const float2 b = fma2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]), sc2, make_float2(-l4.z, -l4.w));
-          pr[4 * c4 + 0] = ex2(a.x);
-          pr[4 * c4 + 1] = ex2(a.y);
-          pr[4 * c4 + 2] = ex2(b.x);
-          pr[4 * c4 + 3] = ex2(b.y);
+    for (int w = blockIdx.x; ok && w < nitems; w += gridDim.x) {
+      const DkdvItem it = dkdv_item(p, w);
+      if (!it.valid) continue;
+      const Seq& sq = it.sq;
+      const int hk = it.hk, z = it.z;
+      const int n = it.n0 + r;
+      if (it.niter == 0) {          // no query attends to these keys
+        if (wg == 0 && n < sq.sk) {
+          T* dkp = reinterpret_cast<T*>(p.dk.ptr) + (int64_t)sq.bidx * p.dk.s[0] + (int64_t)hk * p.dk.s[1] +
+                   (sq.k0 + n) * p.dk.s[2];
+          T* dvp = reinterpret_cast<T*>(p.dv.ptr) + (int64_t)sq.bidx * p.dv.s[0] + (int64_t)hk * p.dv.s[1] +
+                   (sq.k0 + n) * p.dv.s[2];
+          for (int c = 0; c < p.dqk; ++c) dkp[c] = from_f32<T>(0.f);
+          for (int c = 0; c < p.dvo; ++c) dvp[c] = from_f32<T>(0.f);
         }
-      } else {
+        __syncwarp();
+        continue;
+      }
+      int col_lo = 0, col_hi = sq.sq - 1;     // valid query rows for this key
+      if (p.causal) {
+        int64_t lo = (int64_t)n - sq.wr, hi = (int64_t)n + sq.wl;
+        if (lo > col_lo) col_lo = (int)(lo > 0x7fffffffLL ? 0x7fffffffLL : lo);
+        if (hi < col_hi) col_hi = (int)(hi < -1 ? -1 : hi);
+      }
+      if (n >= sq.sk) { col_lo = 1; col_hi = 0; }
+      for (int i = 0; i < it.niter; ++i, ++G) {
+        const int s = (int)(G & 1u);
+        const uint32_t par = G & 1u;
+        const int h = hk * p.group + i / it.nmb;
+        const int mbase = (it.mb_lo + i % it.nmb) * kBlk + cbase;    // first query row of this thread's columns
+        const float* lse2 = aux + s * 256 + cbase;
+        const float* dlt = lse2 + 128;
+        if (!mbar_wait(&bars[L::bAuxFull + s], (G >> 1) & 1u, abort_flag, status, 0x1700)) { ok = false; break; }
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 4);
+        if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x1800)) { ok = false; break; }
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 0);
+        tc_fence_after();
+        float pr[32];
+        tmem_ld32f(tmem_base + lane_addr + kColS + cbase, pr);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[L::bSRead]);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 6);
+        const bool need_mask = !(mbase >= col_lo && mbase + kWgCols - 1 <= col_hi);
+        const bool any_mask = __any_sync(0xffffffffu, need_mask);
+        // exponent arguments: scaled score (+ bias) minus the row's logsumexp, all in log2 units.
+        // Common case: one packed FMA per two elements.  With bias, or when the logsumexp is so
+        // large that product rounding matters (the aux warp flags that), scale first and subtract
+        // second, so that the forward's reference point cancels exactly.
+        if (!p.has_bias && aux_flag[s] == 0) {
+          const float2 sc2 = make_float2(p.qk_scale, p.qk_scale);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
-        if (p.has_bias && n < sq.sk) {
-          const T* bcol = reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
-                          (int64_t)h * p.bias.s[1] + (int64_t)n * p.bias.s[3];
+          for (int c4 = 0; c4 < 8; ++c4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
+            const float2 a = fma2(make_float2(pr[4 * c4], pr[4 * c4 + 1]), sc2, make_float2(-l4.x, -l4.y));
+            const float2 b = fma2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]), sc2, make_float2(-l4.z, -l4.w));
+            pr[4 * c4 + 0] = ex2(a.x);
+            pr[4 * c4 + 1] = ex2(a.y);
+            pr[4 * c4 + 2] = ex2(b.x);
+            pr[4 * c4 + 3] = ex2(b.y);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
+          if (p.has_bias && n < sq.sk) {
+            const T* bcol = reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
+                            (int64_t)h * p.bias.s[1] + (int64_t)n * p.bias.s[3];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int m = mbase + c;
+              if (m < sq.sq) pr[c] = fmaf(to_f32<T>(bcol[(int64_t)m * p.bias.s[2]]), kLog2e, pr[c]);
+            }
+          }
+          __syncwarp();   // lanes beyond the sequence skipped the loads
+#pragma unroll
+          for (int c4 = 0; c4 < 8; ++c4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
+            pr[4 * c4 + 0] = ex2(pr[4 * c4 + 0] - l4.x);
+            pr[4 * c4 + 1] = ex2(pr[4 * c4 + 1] - l4.y);
+            pr[4 * c4 + 2] = ex2(pr[4 * c4 + 2] - l4.z);
+            pr[4 * c4 + 3] = ex2(pr[4 * c4 + 3] - l4.w);
+          }
+        }
+        if (any_mask) {
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int m = mbase + c;
-            if (m < sq.sq) pr[c] = fmaf(to_f32<T>(bcol[(int64_t)m * p.bias.s[2]]), kLog2e, pr[c]);
+            pr[c] = (m >= col_lo && m <= col_hi) ? pr[c] : 0.f;
           }
         }
-        __syncwarp();   // lanes beyond the sequence skipped the loads
-#pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
-          pr[4 * c4 + 0] = ex2(pr[4 * c4 + 0] - l4.x);
-          pr[4 * c4 + 1] = ex2(pr[4 * c4 + 1] - l4.y);
-          pr[4 * c4 + 2] = ex2(pr[4 * c4 + 2] - l4.z);
-          pr[4 * c4 + 3] = ex2(pr[4 * c4 + 3] - l4.w);
-        }
-      }
-      if (any_mask) {
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int m = mbase + c;
-          pr[c] = (m >= col_lo && m <= col_hi) ? pr[c] : 0.f;
-        }
-      }
-      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 7);
-      uint32_t keep = 0xffffffffu;
-      if (p.dropout_on) {
-        const DropoutCtx dctx = dropout_ctx(p, z, h);
-        const int nn = min(n, p.max_sk - 1);
-        keep = 0u;
-#pragma unroll
-        for (int c = 0; c < 32; ++c)
-          if (dropout_keep(dctx, min(mbase + c, p.max_sq - 1), nn)) keep |= (1u << c);
-      }
-      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 1);
-      if (!mbar_wait(&bars[L::bDpFull], par, abort_flag, status, 0x1900 + i)) { ok = false; break; }
-      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 2);
-      tc_fence_after();
-      {
-        float dp[32];
-        tmem_ld32f(tmem_base + lane_addr + kColDP + cbase, dp);
-        tmem_wait_ld();
-        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 10);
-        // This thread has now read its 32 columns of dP: they can take P^T (packed, 16 columns)
-        // followed by dS^T (packed, 16 columns).
-        uint32_t pk[16];
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          float a = pr[2 * c], b = pr[2 * c + 1];
-          if (p.dropout_on) {
-            a = ((keep >> (2 * c)) & 1u) ? a * p.dropout_scale : 0.f;
-            b = ((keep >> (2 * c + 1)) & 1u) ? b * p.dropout_scale : 0.f;
-          }
-          pk[c] = pack2<T>(a, b);
-        }
-        tmem_st16(tmem_base + lane_addr + kColDP + cbase, pk);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 7);
+        uint32_t keep = 0xffffffffu;
         if (p.dropout_on) {
+          const DropoutCtx dctx = dropout_ctx(p, z, h);
+          const int nn = min(n, p.max_sk - 1);
+          keep = 0u;
 #pragma unroll
-          for (int c = 0; c < 32; ++c) dp[c] = ((keep >> c) & 1u) ? dp[c] * p.dropout_scale : 0.f;
+          for (int c = 0; c < 32; ++c)
+            if (dropout_keep(dctx, min(mbase + c, p.max_sq - 1), nn)) keep |= (1u << c);
         }
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 1);
+        if (!mbar_wait(&bars[L::bDpFull], par, abort_flag, status, 0x1900)) { ok = false; break; }
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 2);
+        tc_fence_after();
+        {
+          float dp[32];
+          tmem_ld32f(tmem_base + lane_addr + kColDP + cbase, dp);
+          tmem_wait_ld();
+          if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 10);
+          // This thread has now read its 32 columns of dP: they can take P^T (packed, 16 columns)
+          // followed by dS^T (packed, 16 columns).
+          uint32_t pk[16];
 #pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 d4 = *reinterpret_cast<const float4*>(dlt + 4 * c4);
-          const float2 a = mul2(make_float2(pr[4 * c4], pr[4 * c4 + 1]),
-                                sub2(make_float2(dp[4 * c4], dp[4 * c4 + 1]), make_float2(d4.x, d4.y)));
-          const float2 b = mul2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]),
-                                sub2(make_float2(dp[4 * c4 + 2], dp[4 * c4 + 3]), make_float2(d4.z, d4.w)));
-          pk[2 * c4] = pack2<T>(a.x, a.y);
-          pk[2 * c4 + 1] = pack2<T>(b.x, b.y);
+          for (int c = 0; c < 16; ++c) {
+            float a = pr[2 * c], b = pr[2 * c + 1];
+            if (p.dropout_on) {
+              a = ((keep >> (2 * c)) & 1u) ? a * p.dropout_scale : 0.f;
+              b = ((keep >> (2 * c + 1)) & 1u) ? b * p.dropout_scale : 0.f;
+            }
+            pk[c] = pack2<T>(a, b);
+          }
+          tmem_st16(tmem_base + lane_addr + kColDP + cbase, pk);
+          if (p.dropout_on) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) dp[c] = ((keep >> c) & 1u) ? dp[c] * p.dropout_scale : 0.f;
+          }
+#pragma unroll
+          for (int c4 = 0; c4 < 8; ++c4) {
+            const float4 d4 = *reinterpret_cast<const float4*>(dlt + 4 * c4);
+            const float2 a = mul2(make_float2(pr[4 * c4], pr[4 * c4 + 1]),
+                                  sub2(make_float2(dp[4 * c4], dp[4 * c4 + 1]), make_float2(d4.x, d4.y)));
+            const float2 b = mul2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]),
+                                  sub2(make_float2(dp[4 * c4 + 2], dp[4 * c4 + 3]), make_float2(d4.z, d4.w)));
+            pk[2 * c4] = pack2<T>(a.x, a.y);
+            pk[2 * c4 + 1] = pack2<T>(b.x, b.y);
+          }
+          tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16, pk);
         }
-        tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16, pk);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 11);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars[L::bDsFull]);
+          mbar_arrive(&bars[L::bAuxEmpty + s]);
+        }
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 3);
       }
-      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 11);
-      tmem_wait_st();
-      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 12);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&bars[L::bDsFull]);
-        mbar_arrive(&bars[L::bAuxEmpty + s]);
+      if (!ok) break;
+      // ---- this item's dV and dK: wait for the last two GEMMs, read out, store ----
+      if (!mbar_wait(&bars[L::bAccDone], live & 1u, abort_flag, status, 0x1A00)) { ok = false; break; }
+      ++live;
+      if (wg < HD / 32) {
+        tc_fence_after();
+        T* dvp = reinterpret_cast<T*>(p.dv.ptr) + (int64_t)sq.bidx * p.dv.s[0] + (int64_t)hk * p.dv.s[1] +
+                 (sq.k0 + n) * p.dv.s[2];
+        T* dkp = reinterpret_cast<T*>(p.dk.ptr) + (int64_t)sq.bidx * p.dk.s[0] + (int64_t)hk * p.dk.s[1] +
+                 (sq.k0 + n) * p.dk.s[2];
+        float v[32];
+        const int d0 = wg * 32;
+        tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
+        tmem_wait_ld();
+        if (n < sq.sk) store_row_chunk32<T>(dvp, v, 1.0f, d0, p.dvo);
+        __syncwarp();
+        tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
+        tmem_wait_ld();
+        if (n < sq.sk) store_row_chunk32<T>(dkp, v, p.sm_scale, d0, p.dqk);
+        __syncwarp();
+        // The accumulators are in registers now: the next item's first dV/dK GEMMs (which start from
+        // zero) are only issued after this thread's next hand-off, i.e. after these loads.
+        tc_fence_before();
       }
-      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 3);
-    }
-    if (ok) ok = mbar_wait(&bars[L::bAccDone], 0, abort_flag, status, 0x1A00);
-    if (ok && wg < HD / 32) {
-      tc_fence_after();
-      T* dvp = reinterpret_cast<T*>(p.dv.ptr) + (int64_t)sq.bidx * p.dv.s[0] + (int64_t)hk * p.dv.s[1] +
-               (sq.k0 + n) * p.dv.s[2];
-      T* dkp = reinterpret_cast<T*>(p.dk.ptr) + (int64_t)sq.bidx * p.dk.s[0] + (int64_t)hk * p.dk.s[1] +
-               (sq.k0 + n) * p.dk.s[2];
-      float v[32];
-      const int d0 = wg * 32;
-      tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
-      tmem_wait_ld();
-      if (n < sq.sk) store_row_chunk32<T>(dvp, v, 1.0f, d0, p.dvo);
-      __syncwarp();
-      tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
-      tmem_wait_ld();
-      if (n < sq.sk) store_row_chunk32<T>(dkp, v, p.sm_scale, d0, p.dqk);
     }
   }
 
@@ -522,87 +627,122 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
         tma_load_4d(smem + L::kResA + hf * 16384, &tm_q, &bars[L::bResFull], hf * 64, qrow, h, sq.bidx);
         tma_load_4d(smem + L::kResB + hf * 16384, &tm_do, &bars[L::bResFull], hf * 64, qrow, h, sq.bidx);
       }
-      int issued = 0;
+      // K and V travel through separate two-stage rings: a V block is free again as soon as its
+      // dP GEMM has run, a K block only after the dQ GEMM of the same iteration.
+      int issued_k = 0, issued_v = 0;
       for (int i = 0; i < niter; ++i) {
         const int s = i & 1;
         const uint32_t ph = (uint32_t)(i >> 1) & 1u;
         const int krow = (int)(sq.k0 + (int64_t)(jb_lo + i) * kBlk);
-        if (!mbar_wait(&bars[L::bRingEmpty + s], ph ^ 1u, abort_flag, status, 0x2100 + i)) break;
-        mbar_expect_tx(&bars[L::bRingFull + s], 2 * L::kTile);
-        for (int hf = 0; hf < L::kHalves; ++hf) {
-          tma_load_4d(smem + L::kRingA + s * L::kTile + hf * 16384, &tm_k, &bars[L::bRingFull + s], hf * 64, krow, hk,
-                      sq.bidx);
-          tma_load_4d(smem + L::kRingB + s * L::kTile + hf * 16384, &tm_v, &bars[L::bRingFull + s], hf * 64, krow, hk,
-                      sq.bidx);
-        }
-        issued = i + 1;
+        if (!mbar_wait(&bars[L::bVEmpty + s], ph ^ 1u, abort_flag, status, 0x2100 + i)) break;
+        mbar_expect_tx(&bars[L::bVFull + s], L::kTile);
+        for (int hf = 0; hf < L::kHalves; ++hf)
+          tma_load_4d(smem + L::kRingB + s * L::kTile + hf * 16384, &tm_v, &bars[L::bVFull + s], hf * 64, krow, hk, sq.bidx);
+        issued_v = i + 1;
+        if (!mbar_wait(&bars[L::bRingEmpty + s], ph ^ 1u, abort_flag, status, 0x2180 + i)) break;
+        mbar_expect_tx(&bars[L::bRingFull + s], L::kTile);
+        for (int hf = 0; hf < L::kHalves; ++hf)
+          tma_load_4d(smem + L::kRingA + s * L::kTile + hf * 16384, &tm_k, &bars[L::bRingFull + s], hf * 64, krow, hk, sq.bidx);
+        issued_k = i + 1;
       }
       if (*abort_flag) {
         mbar_wait_quiet(&bars[L::bResFull], 0);
-        for (int i = max(0, issued - 2); i < issued; ++i) mbar_wait_quiet(&bars[L::bRingFull + (i & 1)], (uint32_t)(i >> 1) & 1u);
+        for (int i = max(0, issued_k - 2); i < issued_k; ++i) mbar_wait_quiet(&bars[L::bRingFull + (i & 1)], (uint32_t)(i >> 1) & 1u);
+        for (int i = max(0, issued_v - 2); i < issued_v; ++i) mbar_wait_quiet(&bars[L::bVFull + (i & 1)], (uint32_t)(i >> 1) & 1u);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
-      constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
-      constexpr uint32_t kStageStep = L::kTile >> 4;
-      const uint64_t q_km = kmajor_base(smem_u32(smem + L::kResA)), do_km = kmajor_base(smem_u32(smem + L::kResB));
-      const uint64_t k_km = kmajor_base(smem_u32(smem + L::kRingA)), v_km = kmajor_base(smem_u32(smem + L::kRingB));
-      const uint64_t k_mn = mnmajor_base(smem_u32(smem + L::kRingA));
-      auto issue_s = [&](int i) {      // S = Q K_i^T
-        const uint64_t ka = k_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
+    // The whole warp walks the loop and waits; one elected lane issues.  Keeping the control
+    // flow warp-uniform lets the descriptors live in uniform registers, which makes the issue of
+    // a GEMM several times cheaper in issue slots than a single-lane branch.
+    constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
+    constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
+    constexpr uint32_t kStageStep = L::kTile >> 4;
+    const uint64_t q_km = kmajor_base(smem_u32(smem + L::kResA)), do_km = kmajor_base(smem_u32(smem + L::kResB));
+    const uint64_t k_km = kmajor_base(smem_u32(smem + L::kRingA)), v_km = kmajor_base(smem_u32(smem + L::kRingB));
+    const uint64_t k_mn = mnmajor_base(smem_u32(smem + L::kRingA));
+    auto wait = [&](int bar, uint32_t parity, uint32_t where) {
+      return __all_sync(0xffffffffu, mbar_wait(&bars[bar], parity, abort_flag, status, where)) != 0;
+    };
+    auto issue_s = [&](int i) {      // S = Q K_i^T
+      const uint64_t ka = k_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
           mma_ss(tmem_base + kColS, q_km + kmajor_step(kk), ka + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
         mma_commit(&bars[L::bSFull]);
-      };
-      auto issue_dp = [&](int i) {     // dP = dO V_i^T, into dP buffer i & 1
-        const uint64_t va = v_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
-        const uint32_t d = tmem_base + kColDP + (uint32_t)(i & 1) * 128u;
+      }
+      __syncwarp();
+    };
+    auto issue_dp = [&](int i) {     // dP = dO V_i^T, into dP buffer i & 1; frees V's ring stage
+      const uint64_t va = v_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
+      const uint32_t d = tmem_base + kColDP + (uint32_t)(i & 1) * 128u;
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
           mma_ss(d, do_km + kmajor_step(kk), va + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
         mma_commit(&bars[L::bDpFull + (i & 1)]);
-      };
-      bool ok = mbar_wait(&bars[L::bResFull], 0, abort_flag, status, 0x2200) &&
-                mbar_wait(&bars[L::bRingFull + 0], 0, abort_flag, status, 0x2201);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-        issue_dp(0);
+        mma_commit(&bars[L::bVEmpty + (i & 1)]);
       }
-      for (int i = 0; ok && i < niter; ++i) {
-        const int s = i & 1;
-        const uint32_t par = (uint32_t)i & 1u;
-        if (i + 1 < niter) {
-          // S_i has been copied to registers by every compute thread: its buffer is free.
-          if (!mbar_wait(&bars[L::bSRead], par, abort_flag, status, 0x2300 + i)) break;
-          if (!mbar_wait(&bars[L::bRingFull + ((i + 1) & 1)], (uint32_t)((i + 1) >> 1) & 1u, abort_flag, status,
-                         0x2400 + i))
-            break;
+      __syncwarp();
+    };
+    // dP runs two iterations ahead of dQ (two dP buffers), S one ahead: the compute warps never
+    // wait for the tensor pipe in steady state, and the pipe never waits for a K/V copy that was
+    // only released by the GEMM in front of it.
+    bool ok = wait(L::bResFull, 0, 0x2200) && wait(L::bRingFull + 0, 0, 0x2201);
+    if (ok) {
+      tc_fence_after();
+      issue_s(0);
+      ok = wait(L::bVFull + 0, 0, 0x2202);
+    }
+    if (ok) {
+      tc_fence_after();
+      issue_dp(0);
+      if (niter > 1) {
+        ok = wait(L::bVFull + 1, 0, 0x2203);
+        if (ok) {
           tc_fence_after();
-          issue_s(i + 1);
+          issue_dp(1);
         }
-        if (!mbar_wait(&bars[L::bDsFull], par, abort_flag, status, 0x2500 + i)) break;
+      }
+    }
+    for (int i = 0; ok && i < niter; ++i) {
+      const int s = i & 1;
+      const uint32_t par = (uint32_t)i & 1u;
+      if (i + 1 < niter) {
+        // S_i has been copied to registers by every compute thread: its buffer is free.
+        if (!wait(L::bSRead, par, 0x2300 + i)) break;
+        if (!wait(L::bRingFull + ((i + 1) & 1), (uint32_t)((i + 1) >> 1) & 1u, 0x2400 + i)) break;
         tc_fence_after();
-        {   // dQ += dS K_i
-          const uint64_t ka = k_mn + (uint64_t)((uint32_t)s * kStageStep);
-          const uint32_t first = (i > 0) ? 1u : 0u;
-          const uint32_t ds_col = tmem_base + kColDP + (uint32_t)s * 128u;
+        issue_s(i + 1);
+      }
+      // (a compute warp may be a whole iteration ahead of another one, since dP_{i+1} is already
+      // there: the hand-off barrier alternates with the dP buffer)
+      if (!wait(L::bDsFull2 + s, (uint32_t)(i >> 1) & 1u, 0x2500 + i)) break;
+      if (lane == 0) AB200_STAMPQ(i, 5);
+      tc_fence_after();
+      {   // dQ += dS K_i
+        const uint64_t ka = k_mn + (uint64_t)((uint32_t)s * kStageStep);
+        const uint32_t first = (i > 0) ? 1u : 0u;
+        const uint32_t ds_col = tmem_base + kColDP + (uint32_t)s * 128u;
+        if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
             mma_ts(tmem_base + kColAcc1, ds_col + split_a_col(kk), ka + mnmajor_step(kk), kIdescTS,
                    kk > 0 ? 1u : first);
+          mma_commit(&bars[L::bRingEmpty + s]);
         }
-        mma_commit(&bars[L::bRingEmpty + s]);
-        // dP_{i+1} goes behind dQ_i: issued ahead of it (the second dP buffer would allow that)
-        // it delays dQ_i and the release of the K/V stage, which measured slower.
-        if (i + 1 < niter) issue_dp(i + 1);
+        __syncwarp();
       }
-      mma_commit(&bars[L::bAccDone]);
+      if (i + 2 < niter) {   // dP_{i+2} takes the buffer dQ_i has just read (the pipe runs in issue order)
+        if (!wait(L::bVFull + s, (uint32_t)((i + 2) >> 1) & 1u, 0x2580 + i)) break;
+        tc_fence_after();
+        issue_dp(i + 2);
+      }
+      if (lane == 0) AB200_STAMPQ(i, 9);
     }
+    if (elect_one()) mma_commit(&bars[L::bAccDone]);
     __syncwarp();
   } else if (warp >= 4) {
     const int quarter = warp & 3, wg = (warp - 4) >> 2;
@@ -637,6 +777,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       const uint32_t par = (uint32_t)i & 1u;
       const int nbase = (jb_lo + i) * kBlk + cbase;     // first key of this thread's columns
       if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x2600 + i)) { ok = false; break; }
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 0);
       tc_fence_after();
       float pr[32];
       tmem_ld32f(tmem_base + lane_addr + kColS + cbase, pr);
@@ -644,6 +785,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[L::bSRead]);
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 6);
       const bool need_mask = !(nbase >= row_lo && nbase + kWgCols - 1 <= row_hi);
       const bool any_mask = __any_sync(0xffffffffu, need_mask);
       if (simple) {
@@ -682,12 +824,15 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
         for (int c4 = 0; c4 < 8; ++c4) keep |= dropout_keep4(dctx, md, (nbase >> 2) + c4) << (4 * c4);
       }
       const uint32_t dp_col = tmem_base + lane_addr + kColDP + (uint32_t)(i & 1) * 128u + cbase;
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 7);
       if (!mbar_wait(&bars[L::bDpFull + (i & 1)], (uint32_t)(i >> 1) & 1u, abort_flag, status, 0x2700 + i)) { ok = false; break; }
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 2);
       tc_fence_after();
       {
         float dp[32];
         tmem_ld32f(dp_col, dp);
         tmem_wait_ld();
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 10);
         if (p.dropout_on) {
 #pragma unroll
           for (int c = 0; c < 32; ++c) dp[c] = ((keep >> c) & 1u) ? dp[c] * p.dropout_scale : 0.f;
@@ -723,7 +868,8 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[L::bDsFull]);
+      if (lane == 0) mbar_arrive(&bars[L::bDsFull2 + (i & 1)]);
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 3);
     }
     if (ok) ok = mbar_wait(&bars[L::bAccDone], 0, abort_flag, status, 0x2800);
     if (ok && wg < HD / 32) {
@@ -760,8 +906,12 @@ cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st) {
   if (which == 1) {
     e = cudaFuncSetAttribute(sm100_bwd_dkdv_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return e;
-    dim3 grid((p.max_sk + kBlk - 1) / kBlk, p.hk, p.batch);
-    sm100_bwd_dkdv_kernel<T, HD><<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status);
+    const int nitems = ((p.max_sk + kBlk - 1) / kBlk) * ((p.hk * p.batch + 7) / 8) * 8;
+    int dev = 0, sms = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    dim3 grid(nitems < sms ? nitems : sms, 1, 1);     // persistent: one CTA per SM
+    sm100_bwd_dkdv_kernel<T, HD><<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status, nitems);
   } else {
     e = cudaFuncSetAttribute(sm100_bwd_dq_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return e;

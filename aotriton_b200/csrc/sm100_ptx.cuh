@@ -3,6 +3,7 @@
 // tcgen05 MMA issue/commit, TMEM loads/stores, and the shared-memory / instruction
 // descriptors those need.  Nothing here allocates or synchronises on its own.
 #pragma once
+#include <cstdio>
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -58,9 +59,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   const long long t0 = clock64();
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
+    if (*abort_flag) {
+#ifdef AB200_DEBUG_WAITS
+      if ((threadIdx.x & 31) == 0) printf("blk %d,%d,%d warp %d saw abort at %x\n", blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x >> 5, where);
+#endif
+      return false;
+    }
     if (clock64() - t0 > kWaitLimitCycles) break;
   }
+#ifdef AB200_DEBUG_WAITS
+  if ((threadIdx.x & 31) == 0) printf("blk %d,%d,%d warp %d TIMEOUT at %x\n", blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x >> 5, where);
+#endif
   *abort_flag = 1u;
   if (status) atomicCAS(status, 0u, where);
   return false;
