@@ -86,8 +86,7 @@ struct BwdSmem {
   static constexpr int kBars = kAuxFlag + 16;
   static constexpr int bResFull = 0, bRingFull = 1, bRingEmpty = 3, bAuxFull = 5, bAuxEmpty = 7, bSFull = 9,
                        bDpFull = 10 /* two: one per dP buffer in the dQ kernel */, bDsFull = 12, bAccDone = 13, bSRead = 14,
-                       bResEmpty = 15, bVFull = 16 /* dQ kernel: V has a ring of its own */, bVEmpty = 18,
-                       bDsFull2 = 20 /* dQ kernel: one per dP buffer */, bCount = 22;
+                       bResEmpty = 15, bCount = 16;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kDynamic = kAbort + 4 + 1024;
@@ -142,9 +141,6 @@ __device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t*
     mbar_init(&bars[L::bRingEmpty + s], 1);
     mbar_init(&bars[L::bAuxFull + s], 1);
     mbar_init(&bars[L::bAuxEmpty + s], kComputeWarps);
-    mbar_init(&bars[L::bVFull + s], 1);
-    mbar_init(&bars[L::bVEmpty + s], 1);
-    mbar_init(&bars[L::bDsFull2 + s], kComputeWarps);
   }
   mbar_init(&bars[L::bSFull], 1);
   mbar_init(&bars[L::bDpFull], 1);
@@ -264,63 +260,66 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     __syncwarp();
   } else if (warp == 1) {
     // ================================= MMA issuer ====================================
-    if (lane == 0) {
-      constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
-      constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
-      constexpr uint32_t kStageStep = L::kTile >> 4;
-      const uint64_t k_km = kmajor_base(smem_u32(smem + L::kResA)), v_km = kmajor_base(smem_u32(smem + L::kResB));
-      const uint64_t q_km = kmajor_base(smem_u32(smem + L::kRingA)), do_km = kmajor_base(smem_u32(smem + L::kRingB));
-      const uint64_t q_mn = mnmajor_base(smem_u32(smem + L::kRingA)), do_mn = mnmajor_base(smem_u32(smem + L::kRingB));
-      auto issue_s = [&](uint32_t g) {      // S^T = K Q_g^T
-        const uint64_t qa = q_km + (uint64_t)((g & 1u) * kStageStep);
+    // The whole warp walks the loop and waits; one elected lane issues.  With warp-uniform control
+    // flow the descriptors stay in uniform registers and a GEMM costs few issue slots.
+    constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
+    constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
+    constexpr uint32_t kStageStep = L::kTile >> 4;
+    const uint64_t k_km = kmajor_base(smem_u32(smem + L::kResA)), v_km = kmajor_base(smem_u32(smem + L::kResB));
+    const uint64_t q_km = kmajor_base(smem_u32(smem + L::kRingA)), do_km = kmajor_base(smem_u32(smem + L::kRingB));
+    const uint64_t q_mn = mnmajor_base(smem_u32(smem + L::kRingA)), do_mn = mnmajor_base(smem_u32(smem + L::kRingB));
+    auto wait = [&](int bar, uint32_t parity, uint32_t where) {
+      return __all_sync(0xffffffffu, mbar_wait(&bars[bar], parity, abort_flag, status, where)) != 0;
+    };
+    auto issue_s = [&](uint32_t g) {      // S^T = K Q_g^T
+      const uint64_t qa = q_km + (uint64_t)((g & 1u) * kStageStep);
+      if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
+        for (int kk = 0; kk < HD / 16; ++kk)
           mma_ss(tmem_base + kColS, k_km + kmajor_step(kk), qa + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
-          if (kk == 0) AB200_STAMP(g & 255u, 13);
-          if (kk == 3) AB200_STAMP(g & 255u, 12);
-        }
-        AB200_STAMP(g & 255u, 15);
         mma_commit(&bars[L::bSFull]);
-      };
-      auto issue_dp = [&](uint32_t g) {     // dP^T = V dO_g^T
-        const uint64_t da = do_km + (uint64_t)((g & 1u) * kStageStep);
+      }
+      __syncwarp();
+    };
+    // dP^T = V dO_g^T; `release_kv`: these are the last readers of the item's K and V
+    auto issue_dp = [&](uint32_t g, bool release_kv) {
+      const uint64_t da = do_km + (uint64_t)((g & 1u) * kStageStep);
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
           mma_ss(tmem_base + kColDP, v_km + kmajor_step(kk), da + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
         mma_commit(&bars[L::bDpFull]);
-      };
-      uint32_t G = 0, live = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; ok && w < nitems; w += gridDim.x) {
-        const DkdvItem it = dkdv_item(p, w);
-        if (!it.valid || it.niter == 0) continue;
-        // first iteration of the item: K/V resident, Q/dO block landed, S buffer read out by the
-        // compute warps (the dP buffer is released in issue order by the previous item's dV/dK)
-        if (!mbar_wait(&bars[L::bResFull], live & 1u, abort_flag, status, 0x1200)) break;
-        if (G > 0 && !mbar_wait(&bars[L::bSRead], (G - 1) & 1u, abort_flag, status, 0x1201)) break;
-        if (!mbar_wait(&bars[L::bRingFull + (G & 1u)], (G >> 1) & 1u, abort_flag, status, 0x1202)) break;
-        tc_fence_after();
-        issue_s(G);
-        issue_dp(G);
-        if (it.niter == 1) mma_commit(&bars[L::bResEmpty]);
-        for (int i = 0; i < it.niter; ++i, ++G) {
-          const uint32_t s = G & 1u, par = G & 1u;
-          if (i + 1 < it.niter) {
-            // S_g sits in registers of every compute thread: its buffer can take S_{g+1} already.
-            if (!mbar_wait(&bars[L::bSRead], par, abort_flag, status, 0x1300)) { ok = false; break; }
-            if (!mbar_wait(&bars[L::bRingFull + ((G + 1) & 1u)], ((G + 1) >> 1) & 1u, abort_flag, status, 0x1400)) {
-              ok = false;
-              break;
-            }
-            AB200_STAMP(i + 1, 14);
-            tc_fence_after();
-            issue_s(G + 1);
-            AB200_STAMP(i + 1, 8);
-          }
-          if (!mbar_wait(&bars[L::bDsFull], par, abort_flag, status, 0x1500)) { ok = false; break; }
-          AB200_STAMP(i, 5);
+        if (release_kv) mma_commit(&bars[L::bResEmpty]);
+      }
+      __syncwarp();
+    };
+    uint32_t G = 0, live = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; ok && w < nitems; w += gridDim.x) {
+      const DkdvItem it = dkdv_item(p, w);
+      if (!it.valid || it.niter == 0) continue;
+      // first iteration of the item: K/V resident, Q/dO block landed, S buffer read out by the
+      // compute warps (the dP buffer is released in issue order by the previous item's dV/dK)
+      if (!wait(L::bResFull, live & 1u, 0x1200)) break;
+      if (G > 0 && !wait(L::bSRead, (G - 1) & 1u, 0x1201)) break;
+      if (!wait(L::bRingFull + (G & 1u), (G >> 1) & 1u, 0x1202)) break;
+      tc_fence_after();
+      issue_s(G);
+      issue_dp(G, it.niter == 1);
+      for (int i = 0; i < it.niter; ++i, ++G) {
+        const uint32_t s = G & 1u, par = G & 1u;
+        if (i + 1 < it.niter) {
+          // S_g sits in registers of every compute thread: its buffer can take S_{g+1} already.
+          if (!wait(L::bSRead, par, 0x1300)) { ok = false; break; }
+          if (!wait(L::bRingFull + ((G + 1) & 1u), ((G + 1) >> 1) & 1u, 0x1400)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t first = (i > 0) ? 1u : 0u;
+          issue_s(G + 1);
+        }
+        if (!wait(L::bDsFull, par, 0x1500)) { ok = false; break; }
+        if (lane == 0) AB200_STAMP(i, 5);
+        tc_fence_after();
+        const uint32_t first = (i > 0) ? 1u : 0u;
+        if (elect_one()) {
           {   // dV += P^T dO_g   (P^T: first 16 packed columns of each warpgroup's range of the dP buffer)
             const uint64_t da = do_mn + (uint64_t)(s * kStageStep);
 #pragma unroll
@@ -336,18 +335,14 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
                      kk > 0 ? 1u : first);
           }
           mma_commit(&bars[L::bRingEmpty + s]);
-          if (i + 1 < it.niter) {
-            issue_dp(G + 1);
-            AB200_STAMP(i + 1, 9);
-            if (i + 2 == it.niter) mma_commit(&bars[L::bResEmpty]);   // last users of this item's K and V
-          }
+          if (i + 1 == it.niter) mma_commit(&bars[L::bAccDone]);
         }
-        if (!ok) break;
-        mma_commit(&bars[L::bAccDone]);
-        ++live;
+        __syncwarp();
+        if (i + 1 < it.niter) issue_dp(G + 1, i + 2 == it.niter);
       }
+      if (!ok) break;
+      ++live;
     }
-    __syncwarp();
   } else if (warp == 2) {
     // logsumexp (in log2 units) and delta of the streamed query blocks
     uint32_t G = 0;
@@ -576,6 +571,24 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
   }
 }
 
+// Shared memory and barriers of the dQ kernel: Q and dO resident, K through a three-stage ring
+// (a K block is read twice, by S_i early and by dQ_i late), V through a two-stage ring (read once,
+// by dP_i, two iterations ahead of its use).
+template <int HD>
+struct DqSmem {
+  static constexpr int kHalves = HD / 64;
+  static constexpr int kTile = kHalves * 16384;          // 128 rows x HD x 2 bytes
+  static constexpr int kKStages = 3, kVStages = 2;
+  static constexpr int kResA = 0, kResB = kTile;
+  static constexpr int kK = 2 * kTile, kV = kK + kKStages * kTile;
+  static constexpr int kBars = kV + kVStages * kTile;
+  static constexpr int bResFull = 0, bKFull = 1, bKEmpty = 4, bVFull = 7, bVEmpty = 9, bSFull = 11, bSRead = 12,
+                       bDpFull = 13, bDsFull = 15, bAccDone = 17, bCount = 18;
+  static constexpr int kTmemSlot = kBars + bCount * 8;
+  static constexpr int kAbort = kTmemSlot + 4;
+  static constexpr int kDynamic = kAbort + 4 + 1024;
+};
+
 // =========================================================================================
 // dQ (+ dBias).  grid = (cdiv(max_sq, 128), Hq, batch)
 template <typename T, int HD>
@@ -583,7 +596,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tm_q,
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const __grid_constant__ CUtensorMap tm_do, unsigned int* status) {
-  using L = BwdSmem<HD>;
+  using L = DqSmem<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
@@ -607,7 +620,19 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
   const int niter = n_hi / kBlk - jb_lo + 1;
 
   if (threadIdx.x == 0) {
-    init_barriers<HD>(bars, abort_flag);
+    *abort_flag = 0;
+    mbar_init(&bars[L::bResFull], 1);
+    for (int s = 0; s < L::kKStages; ++s) { mbar_init(&bars[L::bKFull + s], 1); mbar_init(&bars[L::bKEmpty + s], 1); }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars[L::bVFull + s], 1);
+      mbar_init(&bars[L::bVEmpty + s], 1);
+      mbar_init(&bars[L::bDpFull + s], 1);
+      mbar_init(&bars[L::bDsFull + s], kComputeWarps);
+    }
+    mbar_init(&bars[L::bSFull], 1);
+    mbar_init(&bars[L::bSRead], kComputeWarps);
+    mbar_init(&bars[L::bAccDone], 1);
+    fence_barrier_init();
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
   }
   if (warp == 1) {
@@ -627,27 +652,25 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
         tma_load_4d(smem + L::kResA + hf * 16384, &tm_q, &bars[L::bResFull], hf * 64, qrow, h, sq.bidx);
         tma_load_4d(smem + L::kResB + hf * 16384, &tm_do, &bars[L::bResFull], hf * 64, qrow, h, sq.bidx);
       }
-      // K and V travel through separate two-stage rings: a V block is free again as soon as its
-      // dP GEMM has run, a K block only after the dQ GEMM of the same iteration.
       int issued_k = 0, issued_v = 0;
       for (int i = 0; i < niter; ++i) {
-        const int s = i & 1;
-        const uint32_t ph = (uint32_t)(i >> 1) & 1u;
+        const int sv = i & 1, sk = i % L::kKStages;
         const int krow = (int)(sq.k0 + (int64_t)(jb_lo + i) * kBlk);
-        if (!mbar_wait(&bars[L::bVEmpty + s], ph ^ 1u, abort_flag, status, 0x2100 + i)) break;
-        mbar_expect_tx(&bars[L::bVFull + s], L::kTile);
+        if (!mbar_wait(&bars[L::bKEmpty + sk], ((uint32_t)(i / L::kKStages) & 1u) ^ 1u, abort_flag, status, 0x2180 + i)) break;
+        mbar_expect_tx(&bars[L::bKFull + sk], L::kTile);
         for (int hf = 0; hf < L::kHalves; ++hf)
-          tma_load_4d(smem + L::kRingB + s * L::kTile + hf * 16384, &tm_v, &bars[L::bVFull + s], hf * 64, krow, hk, sq.bidx);
-        issued_v = i + 1;
-        if (!mbar_wait(&bars[L::bRingEmpty + s], ph ^ 1u, abort_flag, status, 0x2180 + i)) break;
-        mbar_expect_tx(&bars[L::bRingFull + s], L::kTile);
-        for (int hf = 0; hf < L::kHalves; ++hf)
-          tma_load_4d(smem + L::kRingA + s * L::kTile + hf * 16384, &tm_k, &bars[L::bRingFull + s], hf * 64, krow, hk, sq.bidx);
+          tma_load_4d(smem + L::kK + sk * L::kTile + hf * 16384, &tm_k, &bars[L::bKFull + sk], hf * 64, krow, hk, sq.bidx);
         issued_k = i + 1;
+        if (!mbar_wait(&bars[L::bVEmpty + sv], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag, status, 0x2100 + i)) break;
+        mbar_expect_tx(&bars[L::bVFull + sv], L::kTile);
+        for (int hf = 0; hf < L::kHalves; ++hf)
+          tma_load_4d(smem + L::kV + sv * L::kTile + hf * 16384, &tm_v, &bars[L::bVFull + sv], hf * 64, krow, hk, sq.bidx);
+        issued_v = i + 1;
       }
       if (*abort_flag) {
         mbar_wait_quiet(&bars[L::bResFull], 0);
-        for (int i = max(0, issued_k - 2); i < issued_k; ++i) mbar_wait_quiet(&bars[L::bRingFull + (i & 1)], (uint32_t)(i >> 1) & 1u);
+        for (int i = max(0, issued_k - L::kKStages); i < issued_k; ++i)
+          mbar_wait_quiet(&bars[L::bKFull + i % L::kKStages], (uint32_t)(i / L::kKStages) & 1u);
         for (int i = max(0, issued_v - 2); i < issued_v; ++i) mbar_wait_quiet(&bars[L::bVFull + (i & 1)], (uint32_t)(i >> 1) & 1u);
       }
     }
@@ -660,13 +683,13 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
     constexpr uint32_t kStageStep = L::kTile >> 4;
     const uint64_t q_km = kmajor_base(smem_u32(smem + L::kResA)), do_km = kmajor_base(smem_u32(smem + L::kResB));
-    const uint64_t k_km = kmajor_base(smem_u32(smem + L::kRingA)), v_km = kmajor_base(smem_u32(smem + L::kRingB));
-    const uint64_t k_mn = mnmajor_base(smem_u32(smem + L::kRingA));
+    const uint64_t k_km = kmajor_base(smem_u32(smem + L::kK)), v_km = kmajor_base(smem_u32(smem + L::kV));
+    const uint64_t k_mn = mnmajor_base(smem_u32(smem + L::kK));
     auto wait = [&](int bar, uint32_t parity, uint32_t where) {
       return __all_sync(0xffffffffu, mbar_wait(&bars[bar], parity, abort_flag, status, where)) != 0;
     };
     auto issue_s = [&](int i) {      // S = Q K_i^T
-      const uint64_t ka = k_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
+      const uint64_t ka = k_km + (uint64_t)((uint32_t)(i % L::kKStages) * kStageStep);
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
@@ -687,10 +710,11 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       }
       __syncwarp();
     };
-    // dP runs two iterations ahead of dQ (two dP buffers), S one ahead: the compute warps never
-    // wait for the tensor pipe in steady state, and the pipe never waits for a K/V copy that was
-    // only released by the GEMM in front of it.
-    bool ok = wait(L::bResFull, 0, 0x2200) && wait(L::bRingFull + 0, 0, 0x2201);
+    // Order on the tensor pipe: ... dQ_i, S_{i+2}, dP_{i+2}, dQ_{i+1}, ...  S_{i+2} only needs the
+    // compute warps to have copied S_{i+1} out (early in their iteration i+1) and K_{i+2}, which the
+    // third ring stage has brought in already; dP runs two iterations ahead in its two buffers.  In
+    // steady state neither the compute warps nor the pipe wait for the issuing warp.
+    bool ok = wait(L::bResFull, 0, 0x2200) && wait(L::bKFull + 0, 0, 0x2201);
     if (ok) {
       tc_fence_after();
       issue_s(0);
@@ -699,31 +723,28 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     if (ok) {
       tc_fence_after();
       issue_dp(0);
-      if (niter > 1) {
-        ok = wait(L::bVFull + 1, 0, 0x2203);
-        if (ok) {
-          tc_fence_after();
-          issue_dp(1);
-        }
+    }
+    if (ok && niter > 1) {
+      ok = wait(L::bVFull + 1, 0, 0x2203);
+      if (ok) {
+        tc_fence_after();
+        issue_dp(1);
+        ok = wait(L::bSRead, 0, 0x2300) && wait(L::bKFull + 1, 0, 0x2400);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_s(1);
       }
     }
     for (int i = 0; ok && i < niter; ++i) {
       const int s = i & 1;
-      const uint32_t par = (uint32_t)i & 1u;
-      if (i + 1 < niter) {
-        // S_i has been copied to registers by every compute thread: its buffer is free.
-        if (!wait(L::bSRead, par, 0x2300 + i)) break;
-        if (!wait(L::bRingFull + ((i + 1) & 1), (uint32_t)((i + 1) >> 1) & 1u, 0x2400 + i)) break;
-        tc_fence_after();
-        issue_s(i + 1);
-      }
       // (a compute warp may be a whole iteration ahead of another one, since dP_{i+1} is already
       // there: the hand-off barrier alternates with the dP buffer)
-      if (!wait(L::bDsFull2 + s, (uint32_t)(i >> 1) & 1u, 0x2500 + i)) break;
+      if (!wait(L::bDsFull + s, (uint32_t)(i >> 1) & 1u, 0x2500 + i)) break;
       if (lane == 0) AB200_STAMPQ(i, 5);
       tc_fence_after();
       {   // dQ += dS K_i
-        const uint64_t ka = k_mn + (uint64_t)((uint32_t)s * kStageStep);
+        const uint64_t ka = k_mn + (uint64_t)((uint32_t)(i % L::kKStages) * kStageStep);
         const uint32_t first = (i > 0) ? 1u : 0u;
         const uint32_t ds_col = tmem_base + kColDP + (uint32_t)s * 128u;
         if (elect_one()) {
@@ -731,11 +752,18 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
           for (int kk = 0; kk < 8; ++kk)
             mma_ts(tmem_base + kColAcc1, ds_col + split_a_col(kk), ka + mnmajor_step(kk), kIdescTS,
                    kk > 0 ? 1u : first);
-          mma_commit(&bars[L::bRingEmpty + s]);
+          mma_commit(&bars[L::bKEmpty + i % L::kKStages]);
         }
         __syncwarp();
       }
-      if (i + 2 < niter) {   // dP_{i+2} takes the buffer dQ_i has just read (the pipe runs in issue order)
+      if (i + 2 < niter) {
+        // S_{i+1} has been copied to registers by every compute thread: its buffer is free.
+        if (!wait(L::bSRead, (uint32_t)(i + 1) & 1u, 0x2300 + i + 1)) break;
+        if (!wait(L::bKFull + (i + 2) % L::kKStages, (uint32_t)((i + 2) / L::kKStages) & 1u, 0x2400 + i + 2)) break;
+        tc_fence_after();
+        issue_s(i + 2);
+        if (lane == 0) AB200_STAMPQ(i + 2, 8);
+        // dP_{i+2} takes the buffer dQ_i has just read (the pipe runs in issue order)
         if (!wait(L::bVFull + s, (uint32_t)((i + 2) >> 1) & 1u, 0x2580 + i)) break;
         tc_fence_after();
         issue_dp(i + 2);
@@ -776,6 +804,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     for (int i = 0; i < niter; ++i) {
       const uint32_t par = (uint32_t)i & 1u;
       const int nbase = (jb_lo + i) * kBlk + cbase;     // first key of this thread's columns
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 4);
       if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x2600 + i)) { ok = false; break; }
       if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 0);
       tc_fence_after();
@@ -868,7 +897,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[L::bDsFull2 + (i & 1)]);
+      if (lane == 0) mbar_arrive(&bars[L::bDsFull + (i & 1)]);
       if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 3);
     }
     if (ok) ok = mbar_wait(&bars[L::bAccDone], 0, abort_flag, status, 0x2800);
@@ -913,10 +942,10 @@ cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st) {
     dim3 grid(nitems < sms ? nitems : sms, 1, 1);     // persistent: one CTA per SM
     sm100_bwd_dkdv_kernel<T, HD><<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status, nitems);
   } else {
-    e = cudaFuncSetAttribute(sm100_bwd_dq_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    e = cudaFuncSetAttribute(sm100_bwd_dq_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<HD>::kDynamic);
     if (e != cudaSuccess) return e;
     dim3 grid((p.max_sq + kBlk - 1) / kBlk, p.hq, p.batch);
-    sm100_bwd_dq_kernel<T, HD><<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status);
+    sm100_bwd_dq_kernel<T, HD><<<grid, kBwdThreads, DqSmem<HD>::kDynamic, st>>>(p, tq, tk, tv, tdo, status);
   }
   count_launch();
   return cudaGetLastError();

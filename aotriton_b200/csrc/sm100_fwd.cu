@@ -206,18 +206,24 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       __syncwarp();
     } else if (warp == 1) {
       // ================================ MMA issuer ====================================
-      if (lane == 0) {
-        constexpr uint32_t kIdescQK = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
-        constexpr uint32_t kIdescPV = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
-        // Descriptors are built once; a k-step, a tile or a ring stage only moves the 14-bit
-        // start-address field (units of 16 bytes), which cannot carry out of the field.
-        const uint64_t q_desc = smem_desc_sw128(smem_u32(smem + L::kQ), 16, 1024);
-        const uint64_t k_desc = smem_desc_sw128(smem_u32(smem + L::kK), 16, 1024);
-        const uint64_t v_desc = smem_desc_sw128(smem_u32(smem + L::kV), 16384, 1024);
-        constexpr uint32_t kStageStep = L::kTileBytes >> 4;
-        auto issue_qk = [&](int t, int j) {       // S_t = Q_t K_j^T
-          const uint64_t qd = q_desc + (uint64_t)((uint32_t)t * kStageStep);
-          const uint64_t kd = k_desc + (uint64_t)((uint32_t)(j % kStages) * kStageStep);
+      // The whole warp walks the loop and waits; one elected lane issues.  With warp-uniform
+      // control flow the descriptors stay in uniform registers and a GEMM costs few issue slots.
+      constexpr uint32_t kIdescQK = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
+      constexpr uint32_t kIdescPV = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
+      // Descriptors are built once; a k-step, a tile or a ring stage only moves the 14-bit
+      // start-address field (units of 16 bytes), which cannot carry out of the field.
+      const uint64_t q_desc = smem_desc_sw128(smem_u32(smem + L::kQ), 16, 1024);
+      const uint64_t k_desc = smem_desc_sw128(smem_u32(smem + L::kK), 16, 1024);
+      const uint64_t v_desc = smem_desc_sw128(smem_u32(smem + L::kV), 16384, 1024);
+      constexpr uint32_t kStageStep = L::kTileBytes >> 4;
+      auto wait = [&](int bar, uint32_t parity, uint32_t where) {
+        return __all_sync(0xffffffffu, mbar_wait(&bars[bar], parity, abort_flag, status, where)) != 0;
+      };
+      // S_t = Q_t K_j^T; `release_k`: this is the last reader of the K stage
+      auto issue_qk = [&](int t, int j, bool release_k) {
+        const uint64_t qd = q_desc + (uint64_t)((uint32_t)t * kStageStep);
+        const uint64_t kd = k_desc + (uint64_t)((uint32_t)(j % kStages) * kStageStep);
+        if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk) {
             constexpr uint32_t kHalfStep = 16384u >> 4, kInner = 32u >> 4;
@@ -225,31 +231,32 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
             mma_ss(tmem_base + (uint32_t)t * 128u, qd + off, kd + off, kIdescQK, kk > 0 ? 1u : 0u);
           }
           mma_commit(&bars[L::bSFull + t]);
-        };
-        bool ok = true;
-        for (int t = 0; ok && t < ntile; ++t) ok = mbar_wait(&bars[L::bQFull + t], 0, abort_flag, status, 0x300 + t);
-        if (ok) ok = mbar_wait(&bars[L::bKFull + 0], 0, abort_flag, status, 0x400);
-        if (ok) {
-          tc_fence_after();
-          for (int t = 0; t < ntile; ++t) issue_qk(t, 0);
-          mma_commit(&bars[L::bKEmpty + 0]);
+          if (release_k) mma_commit(&bars[L::bKEmpty + (j % kStages)]);
         }
-        for (int j = 0; ok && j < nblk; ++j) {
-          const int s = j % kStages;
-          const uint32_t par = (uint32_t)j & 1u;
-          if (!mbar_wait(&bars[L::bVFull + s], (uint32_t)(j / kStages) & 1u, abort_flag, status, 0x600 + j)) break;
-          if (j + 1 < nblk) {
-            if (!mbar_wait(&bars[L::bKFull + ((j + 1) % kStages)], (uint32_t)((j + 1) / kStages) & 1u, abort_flag,
-                           status, 0x400 + j + 1))
-              break;
-          }
-          const uint64_t vd = v_desc + (uint64_t)((uint32_t)s * kStageStep);
-          const uint32_t first = (j > 0) ? 1u : 0u;
-          for (int t = 0; ok && t < ntile; ++t) {
-            if (!mbar_wait(&bars[L::bPFull + t], par, abort_flag, status, 0x500 + 2 * j + t)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t pcol = tmem_base + (uint32_t)t * 128u;
-            const uint32_t ocol = tmem_base + 256u + (uint32_t)t * 128u;
+        __syncwarp();
+      };
+      bool ok = true;
+      for (int t = 0; ok && t < ntile; ++t) ok = wait(L::bQFull + t, 0, 0x300 + t);
+      if (ok) ok = wait(L::bKFull + 0, 0, 0x400);
+      if (ok) {
+        tc_fence_after();
+        for (int t = 0; t < ntile; ++t) issue_qk(t, 0, t == ntile - 1);
+      }
+      for (int j = 0; ok && j < nblk; ++j) {
+        const int s = j % kStages;
+        const uint32_t par = (uint32_t)j & 1u;
+        if (!wait(L::bVFull + s, (uint32_t)(j / kStages) & 1u, 0x600 + j)) break;
+        if (j + 1 < nblk) {
+          if (!wait(L::bKFull + ((j + 1) % kStages), (uint32_t)((j + 1) / kStages) & 1u, 0x400 + j + 1)) break;
+        }
+        const uint64_t vd = v_desc + (uint64_t)((uint32_t)s * kStageStep);
+        const uint32_t first = (j > 0) ? 1u : 0u;
+        for (int t = 0; ok && t < ntile; ++t) {
+          if (!wait(L::bPFull + t, par, 0x500 + 2 * j + t)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t pcol = tmem_base + (uint32_t)t * 128u;
+          const uint32_t ocol = tmem_base + 256u + (uint32_t)t * 128u;
+          if (elect_one()) {
 #pragma unroll
             for (int kk = 0; kk < kBN / 16; ++kk) {
               // 16 keys per step: 8 packed columns of P, 2048 bytes of V (two 8-key groups)
@@ -257,14 +264,12 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
             }
             mma_commit(&bars[L::bPvDone + t]);
             if (t == ntile - 1) mma_commit(&bars[L::bVEmpty + s]);
-            if (j + 1 < nblk) {
-              issue_qk(t, j + 1);     // the tile's S buffer is free again: PV_t(j), just issued, runs first
-              if (t == ntile - 1) mma_commit(&bars[L::bKEmpty + ((j + 1) % kStages)]);
-            }
           }
+          __syncwarp();
+          // the tile's S buffer is free again: PV_t(j), just issued, runs first
+          if (j + 1 < nblk) issue_qk(t, j + 1, t == ntile - 1);
         }
       }
-      __syncwarp();
     }
   } else {
     // ================================== softmax =====================================
