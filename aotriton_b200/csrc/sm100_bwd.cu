@@ -34,12 +34,19 @@
 //   dK and dQ are multiplied by sm_scale at the end.
 //
 // Every wait is bounded (sm100_ptx.cuh).
+#include <atomic>
 #include "launch.h"
 #include "sm100_ptx.cuh"
 
 namespace ab200 {
 
 __device__ unsigned int g_sm100_bwd_status = 0;
+
+// Ticket counters of the persistent dK/dV kernel.  Each launch takes the next one of the pool and
+// zeroes it in stream order, so launches on different streams do not share a counter unless more
+// than kTicketPool of them are in flight at once.
+constexpr unsigned int kTicketPool = 256;
+__device__ unsigned int g_dkdv_ticket[kTicketPool];
 
 // Optional pipeline trace (compile with -DAB200_TRACE): SM cycle stamps of the hand-offs of the
 // first CTA of the dK/dV kernel, six per iteration, read back with ab200_debug_read_trace().
@@ -81,15 +88,21 @@ struct BwdSmem {
   static constexpr int kTile = kHalves * 16384;          // 128 rows x HD x 2 bytes
   static constexpr int kResA = 0, kResB = kTile;         // resident pair
   static constexpr int kRingA = 2 * kTile, kRingB = 4 * kTile;   // two stages each
-  static constexpr int kAux = 6 * kTile;                 // 2 stages x (128 lse2 + 128 delta) floats
+  static constexpr int kStage = 6 * kTile;               // write-out staging: 128 rows x HD, 16-bit
+  static constexpr int kAux = kStage + kTile;            // 2 stages x (128 lse2 + 128 delta) floats
   static constexpr int kAuxFlag = kAux + 2 * 256 * 4;    // per stage: 1 when some |lse2| is huge
-  static constexpr int kBars = kAuxFlag + 16;
+  static constexpr int kSched = kAuxFlag + 16;             // two slots: next work item of this CTA
+  static constexpr int kBars = kSched + 16;
   static constexpr int bResFull = 0, bRingFull = 1, bRingEmpty = 3, bAuxFull = 5, bAuxEmpty = 7, bSFull = 9,
                        bDpFull = 10 /* two: one per dP buffer in the dQ kernel */, bDsFull = 12, bAccDone = 13, bSRead = 14,
-                       bResEmpty = 15, bCount = 16;
+                       bResEmpty = 15, bPFull = 16, bSchedFull = 17, bSchedEmpty = 19,
+                       bStage = 21, bCount = 22;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
-  static constexpr int kDynamic = kAbort + 4 + 1024;
+  static constexpr int kUsed = kAbort + 4;
+  // The tiles need 1024-byte alignment, which is established at run time; the kernel checks that
+  // the padding it needed still fits (without static shared memory the base is aligned already).
+  static constexpr int kDynamic = kUsed + 512;
 };
 
 // Descriptors are built once per tile base; a k-step or a ring stage only moves the 14-bit
@@ -141,11 +154,15 @@ __device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t*
     mbar_init(&bars[L::bRingEmpty + s], 1);
     mbar_init(&bars[L::bAuxFull + s], 1);
     mbar_init(&bars[L::bAuxEmpty + s], kComputeWarps);
+    mbar_init(&bars[L::bSchedFull + s], 1);
+    mbar_init(&bars[L::bSchedEmpty + s], kComputeWarps + 3);   // compute warps, producer, MMA issuer, aux warp
   }
   mbar_init(&bars[L::bSFull], 1);
   mbar_init(&bars[L::bDpFull], 1);
   mbar_init(&bars[L::bDpFull + 1], 1);
   mbar_init(&bars[L::bDsFull], kComputeWarps);
+  mbar_init(&bars[L::bPFull], kComputeWarps);
+  mbar_init(&bars[L::bStage], kComputeWarps);
   mbar_init(&bars[L::bAccDone], 1);
   mbar_init(&bars[L::bSRead], kComputeWarps);
   mbar_init(&bars[L::bResEmpty], 1);
@@ -194,18 +211,40 @@ template <typename T, int HD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                      const __grid_constant__ CUtensorMap tm_do, unsigned int* status, int nitems) {
+                      const __grid_constant__ CUtensorMap tm_do, unsigned int* status, int nitems,
+                      unsigned int* ticket) {
   using L = BwdSmem<HD>;
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAbort);
   float* aux = reinterpret_cast<float*>(smem + L::kAux);
   volatile uint32_t* aux_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAuxFlag);
+  volatile int* sched = reinterpret_cast<volatile int*>(smem + L::kSched);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
+  if ((int)(smem - smem_raw) + L::kUsed > L::kDynamic) {      // the alignment padding did not fit
+    if (threadIdx.x == 0) atomicCAS(status, 0u, 0x1F00u);
+    return;
+  }
+
+  // Work items are handed out dynamically: the first one is the CTA's index, every further one
+  // comes from a global ticket counter (warp 3 draws it one item ahead and publishes it in a
+  // two-slot ring that every other role reads).  `m` counts the items a role has drawn.
+  auto next_item = [&](uint32_t m, bool whole_warp) -> int {
+    const uint32_t k = m & 1u;
+    if (!mbar_wait(&bars[L::bSchedFull + k], (m >> 1) & 1u, abort_flag, status, 0x1B00)) return 0x7fffffff;
+    const int w = sched[k];
+    if (whole_warp) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[L::bSchedEmpty + k]);
+    } else {
+      mbar_arrive(&bars[L::bSchedEmpty + k]);
+    }
+    return w;
+  };
 
   if (threadIdx.x == 0) {
     init_barriers<HD>(bars, abort_flag);
@@ -223,9 +262,9 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
   if (warp == 0) {
     // ================================ TMA producer ===================================
     if (lane == 0) {
-      uint32_t G = 0, live = 0;
+      uint32_t G = 0, live = 0, drawn = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < nitems; w += gridDim.x) {
+      for (int w = blockIdx.x; ok && w < nitems; w = next_item(drawn++, false)) {
         const DkdvItem it = dkdv_item(p, w);
         if (!it.valid || it.niter == 0) continue;
         // K and V of the previous item are free once its last S and dP GEMMs have run.
@@ -293,9 +332,9 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       }
       __syncwarp();
     };
-    uint32_t G = 0, live = 0;
+    uint32_t G = 0, live = 0, drawn = 0;
     bool ok = true;
-    for (int w = blockIdx.x; ok && w < nitems; w += gridDim.x) {
+    for (int w = blockIdx.x; ok && w < nitems; w = next_item(drawn++, true)) {
       const DkdvItem it = dkdv_item(p, w);
       if (!it.valid || it.niter == 0) continue;
       // first iteration of the item: K/V resident, Q/dO block landed, S buffer read out by the
@@ -303,9 +342,11 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       if (!wait(L::bResFull, live & 1u, 0x1200)) break;
       if (G > 0 && !wait(L::bSRead, (G - 1) & 1u, 0x1201)) break;
       if (!wait(L::bRingFull + (G & 1u), (G >> 1) & 1u, 0x1202)) break;
+      if (lane == 0) AB200_STAMP(G, 15);
       tc_fence_after();
       issue_s(G);
       issue_dp(G, it.niter == 1);
+      if (lane == 0) AB200_STAMP(G, 8);
       for (int i = 0; i < it.niter; ++i, ++G) {
         const uint32_t s = G & 1u, par = G & 1u;
         if (i + 1 < it.niter) {
@@ -315,25 +356,27 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           tc_fence_after();
           issue_s(G + 1);
         }
-        if (!wait(L::bDsFull, par, 0x1500)) { ok = false; break; }
-        if (lane == 0) AB200_STAMP(i, 5);
-        tc_fence_after();
         const uint32_t first = (i > 0) ? 1u : 0u;
-        if (elect_one()) {
-          {   // dV += P^T dO_g   (P^T: first 16 packed columns of each warpgroup's range of the dP buffer)
-            const uint64_t da = do_mn + (uint64_t)(s * kStageStep);
+        // P^T is handed over ahead of dS^T (it does not need the dS arithmetic): dV runs meanwhile
+        if (!wait(L::bPFull, par, 0x1480)) { ok = false; break; }
+        tc_fence_after();
+        if (elect_one()) {   // dV += P^T dO_g   (P^T: first 16 packed columns of each warpgroup's range of the dP buffer)
+          const uint64_t da = do_mn + (uint64_t)(s * kStageStep);
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              mma_ts(tmem_base + kColAcc0, tmem_base + kColDP + split_a_col(kk), da + mnmajor_step(kk), kIdescTS,
-                     kk > 0 ? 1u : first);
-          }
-          {   // dK += dS^T Q_g  (dS^T: the next 16 packed columns)
-            const uint64_t qa = q_mn + (uint64_t)(s * kStageStep);
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts(tmem_base + kColAcc0, tmem_base + kColDP + split_a_col(kk), da + mnmajor_step(kk), kIdescTS,
+                   kk > 0 ? 1u : first);
+        }
+        __syncwarp();
+        if (!wait(L::bDsFull, par, 0x1500)) { ok = false; break; }
+        if (lane == 0) AB200_STAMP(G, 5);
+        tc_fence_after();
+        if (elect_one()) {   // dK += dS^T Q_g  (dS^T: the next 16 packed columns)
+          const uint64_t qa = q_mn + (uint64_t)(s * kStageStep);
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + 16u + split_a_col(kk), qa + mnmajor_step(kk), kIdescTS,
-                     kk > 0 ? 1u : first);
-          }
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + 16u + split_a_col(kk), qa + mnmajor_step(kk), kIdescTS,
+                   kk > 0 ? 1u : first);
           mma_commit(&bars[L::bRingEmpty + s]);
           if (i + 1 == it.niter) mma_commit(&bars[L::bAccDone]);
         }
@@ -345,9 +388,9 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     }
   } else if (warp == 2) {
     // logsumexp (in log2 units) and delta of the streamed query blocks
-    uint32_t G = 0;
+    uint32_t G = 0, drawn = 0;
     bool ok = true;
-    for (int w = blockIdx.x; ok && w < nitems; w += gridDim.x) {
+    for (int w = blockIdx.x; ok && w < nitems; w = next_item(drawn++, true)) {
       const DkdvItem it = dkdv_item(p, w);
       if (!it.valid || it.niter == 0) continue;
       for (int i = 0; i < it.niter; ++i, ++G) {
@@ -379,15 +422,37 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         if (lane == 0) mbar_arrive(&bars[L::bAuxFull + s]);
       }
     }
+  } else if (warp == 3) {
+    // ================================= scheduler =====================================
+    if (lane == 0) {
+      for (uint32_t m = 0;; ++m) {
+        const uint32_t k = m & 1u;
+        if (!mbar_wait(&bars[L::bSchedEmpty + k], ((m >> 1) & 1u) ^ 1u, abort_flag, status, 0x1C00)) break;
+        const unsigned int t = atomicAdd(ticket, 1u);
+        const int w = t < 0x40000000u ? (int)(gridDim.x + t) : 0x7fffffff;
+        sched[k] = w;
+        mbar_arrive(&bars[L::bSchedFull + k]);
+        if (w >= nitems) break;
+      }
+    }
+    __syncwarp();
   } else if (warp >= 4) {
     // ================================== compute ======================================
     const int quarter = warp & 3, wg = (warp - 4) >> 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int cbase = kWgCols * wg;
-    uint32_t G = 0, live = 0;
+    uint32_t G = 0, live = 0, drawn = 0, sph = 0;
     bool ok = true;
-    for (int w = blockIdx.x; ok && w < nitems; w += gridDim.x) {
+    // barrier among the compute warps (bounded like every other wait)
+    auto stage_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[L::bStage]);
+      const bool good = mbar_wait(&bars[L::bStage], sph & 1u, abort_flag, status, 0x1D00);
+      ++sph;
+      return good;
+    };
+    for (int w = blockIdx.x; ok && w < nitems; w = next_item(drawn++, true)) {
       const DkdvItem it = dkdv_item(p, w);
       if (!it.valid) continue;
       const Seq& sq = it.sq;
@@ -420,9 +485,9 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         const float* lse2 = aux + s * 256 + cbase;
         const float* dlt = lse2 + 128;
         if (!mbar_wait(&bars[L::bAuxFull + s], (G >> 1) & 1u, abort_flag, status, 0x1700)) { ok = false; break; }
-        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 4);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 4);
         if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x1800)) { ok = false; break; }
-        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 0);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 0);
         tc_fence_after();
         float pr[32];
         tmem_ld32f(tmem_base + lane_addr + kColS + cbase, pr);
@@ -430,7 +495,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[L::bSRead]);
-        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 6);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 6);
         const bool need_mask = !(mbase >= col_lo && mbase + kWgCols - 1 <= col_hi);
         const bool any_mask = __any_sync(0xffffffffu, need_mask);
         // exponent arguments: scaled score (+ bias) minus the row's logsumexp, all in log2 units.
@@ -478,7 +543,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
             pr[c] = (m >= col_lo && m <= col_hi) ? pr[c] : 0.f;
           }
         }
-        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 7);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 7);
         uint32_t keep = 0xffffffffu;
         if (p.dropout_on) {
           const DropoutCtx dctx = dropout_ctx(p, z, h);
@@ -488,15 +553,15 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           for (int c = 0; c < 32; ++c)
             if (dropout_keep(dctx, min(mbase + c, p.max_sq - 1), nn)) keep |= (1u << c);
         }
-        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 1);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 1);
         if (!mbar_wait(&bars[L::bDpFull], par, abort_flag, status, 0x1900)) { ok = false; break; }
-        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 2);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 2);
         tc_fence_after();
         {
           float dp[32];
           tmem_ld32f(tmem_base + lane_addr + kColDP + cbase, dp);
           tmem_wait_ld();
-          if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 10);
+          if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 10);
           // This thread has now read its 32 columns of dP: they can take P^T (packed, 16 columns)
           // followed by dS^T (packed, 16 columns).
           uint32_t pk[16];
@@ -510,6 +575,10 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
             pk[c] = pack2<T>(a, b);
           }
           tmem_st16(tmem_base + lane_addr + kColDP + cbase, pk);
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[L::bPFull]);
           if (p.dropout_on) {
 #pragma unroll
             for (int c = 0; c < 32; ++c) dp[c] = ((keep >> c) & 1u) ? dp[c] * p.dropout_scale : 0.f;
@@ -526,7 +595,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           }
           tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16, pk);
         }
-        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 11);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 11);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -534,31 +603,45 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           mbar_arrive(&bars[L::bDsFull]);
           mbar_arrive(&bars[L::bAuxEmpty + s]);
         }
-        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(i, 3);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 3);
       }
       if (!ok) break;
       // ---- this item's dV and dK: wait for the last two GEMMs, read out, store ----
       if (!mbar_wait(&bars[L::bAccDone], live & 1u, abort_flag, status, 0x1A00)) { ok = false; break; }
+      if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G - 1, 13);
       ++live;
-      if (wg < HD / 32) {
-        tc_fence_after();
-        T* dvp = reinterpret_cast<T*>(p.dv.ptr) + (int64_t)sq.bidx * p.dv.s[0] + (int64_t)hk * p.dv.s[1] +
-                 (sq.k0 + n) * p.dv.s[2];
-        T* dkp = reinterpret_cast<T*>(p.dk.ptr) + (int64_t)sq.bidx * p.dk.s[0] + (int64_t)hk * p.dk.s[1] +
-                 (sq.k0 + n) * p.dk.s[2];
-        float v[32];
+      {
+        // Rows go through a staging tile so that the global stores are whole rows per warp.
+        uint8_t* stage = smem + L::kStage;
+        const int tid = (int)threadIdx.x - 128, nrows = min(kBlk, sq.sk - it.n0);
         const int d0 = wg * 32;
-        tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
-        tmem_wait_ld();
-        if (n < sq.sk) store_row_chunk32<T>(dvp, v, 1.0f, d0, p.dvo);
-        __syncwarp();
-        tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
-        tmem_wait_ld();
-        if (n < sq.sk) store_row_chunk32<T>(dkp, v, p.sm_scale, d0, p.dqk);
-        __syncwarp();
+        float v[32];
+        tc_fence_after();
+        if (wg < HD / 32) {
+          tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
+          tmem_wait_ld();
+          stage_put32<T>(stage, r, d0, v, 1.0f, HD * 2);
+        }
+        if (!stage_sync()) { ok = false; break; }
+        stage_copy_out<T>(stage, reinterpret_cast<T*>(p.dv.ptr) + (int64_t)sq.bidx * p.dv.s[0] + (int64_t)hk * p.dv.s[1] +
+                                     (sq.k0 + it.n0) * p.dv.s[2],
+                          p.dv.s[2], nrows, p.dvo, tid, kComputeWarps * 32, HD * 2);
+        if (wg < HD / 32) {
+          tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
+          tmem_wait_ld();
+        }
         // The accumulators are in registers now: the next item's first dV/dK GEMMs (which start from
         // zero) are only issued after this thread's next hand-off, i.e. after these loads.
         tc_fence_before();
+        if (!stage_sync()) { ok = false; break; }       // everyone has read dV out of the staging tile
+        if (wg < HD / 32) stage_put32<T>(stage, r, d0, v, p.sm_scale, HD * 2);
+        if (!stage_sync()) { ok = false; break; }
+        stage_copy_out<T>(stage, reinterpret_cast<T*>(p.dk.ptr) + (int64_t)sq.bidx * p.dk.s[0] + (int64_t)hk * p.dk.s[1] +
+                                     (sq.k0 + it.n0) * p.dk.s[2],
+                          p.dk.s[2], nrows, p.dqk, tid, kComputeWarps * 32, HD * 2);
+        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G - 1, 14);
+        // (the staging tile is next written after this item's successor has had all its hand-offs,
+        // which every warp makes after this point)
       }
     }
   }
@@ -583,7 +666,7 @@ struct DqSmem {
   static constexpr int kK = 2 * kTile, kV = kK + kKStages * kTile;
   static constexpr int kBars = kV + kVStages * kTile;
   static constexpr int bResFull = 0, bKFull = 1, bKEmpty = 4, bVFull = 7, bVEmpty = 9, bSFull = 11, bSRead = 12,
-                       bDpFull = 13, bDsFull = 15, bAccDone = 17, bCount = 18;
+                       bDpFull = 13, bDsFull = 15, bAccDone = 17, bStage = 18, bCount = 19;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kDynamic = kAbort + 4 + 1024;
@@ -632,6 +715,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     mbar_init(&bars[L::bSFull], 1);
     mbar_init(&bars[L::bSRead], kComputeWarps);
     mbar_init(&bars[L::bAccDone], 1);
+    mbar_init(&bars[L::bStage], kComputeWarps);
     fence_barrier_init();
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
   }
@@ -901,15 +985,23 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 3);
     }
     if (ok) ok = mbar_wait(&bars[L::bAccDone], 0, abort_flag, status, 0x2800);
-    if (ok && wg < HD / 32) {
-      tc_fence_after();
-      T* dqp = reinterpret_cast<T*>(p.dq.ptr) + (int64_t)sq.bidx * p.dq.s[0] + (int64_t)h * p.dq.s[1] +
-               (sq.q0 + m) * p.dq.s[2];
-      float v[32];
-      const int d0 = wg * 32;
-      tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
-      tmem_wait_ld();
-      if (m < sq.sq) store_row_chunk32<T>(dqp, v, p.sm_scale, d0, p.dqk);
+    if (ok) {
+      // dQ rows go through the (now idle) Q tile so that the global stores are whole rows per warp
+      uint8_t* stage = smem + L::kResA;
+      if (wg < HD / 32) {
+        tc_fence_after();
+        float v[32];
+        const int d0 = wg * 32;
+        tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
+        tmem_wait_ld();
+        stage_put32<T>(stage, r, d0, v, p.sm_scale, HD * 2);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[L::bStage]);
+      if (mbar_wait(&bars[L::bStage], 0, abort_flag, status, 0x2900))
+        stage_copy_out<T>(stage, reinterpret_cast<T*>(p.dq.ptr) + (int64_t)sq.bidx * p.dq.s[0] + (int64_t)h * p.dq.s[1] +
+                                     (sq.q0 + m0) * p.dq.s[2],
+                          p.dq.s[2], min(kBlk, sq.sq - m0), p.dqk, (int)threadIdx.x - 128, kComputeWarps * 32, HD * 2);
     }
   }
 
@@ -940,7 +1032,13 @@ cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st) {
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
     if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
     dim3 grid(nitems < sms ? nitems : sms, 1, 1);     // persistent: one CTA per SM
-    sm100_bwd_dkdv_kernel<T, HD><<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status, nitems);
+    // ticket counter of this launch: one of a small pool, zeroed in stream order
+    static std::atomic<unsigned int> launch_seq{0};
+    unsigned int* tickets = nullptr;
+    if ((e = cudaGetSymbolAddress(reinterpret_cast<void**>(&tickets), g_dkdv_ticket)) != cudaSuccess) return e;
+    unsigned int* ticket = tickets + (launch_seq.fetch_add(1) % kTicketPool);
+    if ((e = cudaMemsetAsync(ticket, 0, sizeof(unsigned int), st)) != cudaSuccess) return e;
+    sm100_bwd_dkdv_kernel<T, HD><<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status, nitems, ticket);
   } else {
     e = cudaFuncSetAttribute(sm100_bwd_dq_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<HD>::kDynamic);
     if (e != cudaSuccess) return e;

@@ -330,6 +330,48 @@ inline EncodeTiledFn tensor_map_encoder() {
   return fn;
 }
 
+// ---- coalesced write-out of a [128 rows x D] 16-bit tile through shared memory -------------
+// A thread that owns one row of a tile (a TMEM lane) would store 16 bytes per instruction at a
+// row stride: 32 separate memory lines per warp instruction, which costs thousands of cycles per
+// tile.  Instead the rows go to a staging tile and are written out with whole rows per warp.
+// Staging layout: row r starts at r * row_bytes; 16-byte chunk c of the row sits at position
+// (c & ~7) | ((c ^ r) & 7), which makes both the row-per-thread writes and the chunk-per-thread
+// reads free of bank conflicts.
+__device__ __forceinline__ uint32_t stage_chunk_offset(int r, int c, int row_bytes) {
+  return (uint32_t)(r * row_bytes + (((c & ~7) | ((c ^ r) & 7)) << 4));
+}
+// 32 consecutive values (columns d0..d0+31, d0 a multiple of 32) of row r
+template <typename T>
+__device__ __forceinline__ void stage_put32(uint8_t* stage, int r, int d0, const float* v, float scale, int row_bytes) {
+#pragma unroll
+  for (int v8 = 0; v8 < 4; ++v8) {
+    uint4 w;
+    w.x = pack2<T>(v[v8 * 8 + 0] * scale, v[v8 * 8 + 1] * scale);
+    w.y = pack2<T>(v[v8 * 8 + 2] * scale, v[v8 * 8 + 3] * scale);
+    w.z = pack2<T>(v[v8 * 8 + 4] * scale, v[v8 * 8 + 5] * scale);
+    w.w = pack2<T>(v[v8 * 8 + 6] * scale, v[v8 * 8 + 7] * scale);
+    *reinterpret_cast<uint4*>(stage + stage_chunk_offset(r, (d0 >> 3) + v8, row_bytes)) = w;
+  }
+}
+// `tile` points at row 0 of the tile in global memory (rows `row_stride` elements apart, 16-byte
+// aligned); the first `nrows` rows and `dmax` columns (a multiple of 8) are written.
+template <typename T>
+__device__ __forceinline__ void stage_copy_out(const uint8_t* stage, T* tile, int64_t row_stride, int nrows, int dmax,
+                                               int tid, int nthreads, int row_bytes) {
+  const int cpr = row_bytes >> 4;      // chunks per row: 8 or 16
+  const int shift = (cpr == 16) ? 4 : 3;
+  for (int idx = tid; idx < 128 * cpr; idx += nthreads) {
+    const int r = idx >> shift, c = idx & (cpr - 1);
+    if (r < nrows && c * 8 < dmax)
+      *reinterpret_cast<uint4*>(tile + (int64_t)r * row_stride + c * 8) =
+          *reinterpret_cast<const uint4*>(stage + stage_chunk_offset(r, c, row_bytes));
+  }
+}
+// Barrier among `nthreads` threads (a multiple of 32) of the CTA; id 0 is __syncthreads.
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 // Tile map over a (B, H, S, D) view of 16-bit elements: box = 64 columns x `box_rows` rows,
 // 128-byte swizzle, zero fill outside the extents.  Dimensions are given innermost first.
 inline bool make_tile_map_16bit(CUtensorMap* out, const View4& v, int64_t d_extent, int64_t s_extent, int box_rows) {
