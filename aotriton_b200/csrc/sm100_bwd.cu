@@ -96,7 +96,7 @@ struct BwdSmem {
   static constexpr int bResFull = 0, bRingFull = 1, bRingEmpty = 3, bAuxFull = 5, bAuxEmpty = 7, bSFull = 9,
                        bDpFull = 10 /* two: one per dP buffer in the dQ kernel */, bDsFull = 12, bAccDone = 13, bSRead = 14,
                        bResEmpty = 15, bPFull = 16, bSchedFull = 17, bSchedEmpty = 19,
-                       bStage = 21, bCount = 22;
+                       bCount = 21;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kUsed = kAbort + 4;
@@ -162,7 +162,6 @@ __device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t*
   mbar_init(&bars[L::bDpFull + 1], 1);
   mbar_init(&bars[L::bDsFull], kComputeWarps);
   mbar_init(&bars[L::bPFull], kComputeWarps);
-  mbar_init(&bars[L::bStage], kComputeWarps);
   mbar_init(&bars[L::bAccDone], 1);
   mbar_init(&bars[L::bSRead], kComputeWarps);
   mbar_init(&bars[L::bResEmpty], 1);
@@ -442,16 +441,8 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     const int r = quarter * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int cbase = kWgCols * wg;
-    uint32_t G = 0, live = 0, drawn = 0, sph = 0;
+    uint32_t G = 0, live = 0, drawn = 0;
     bool ok = true;
-    // barrier among the compute warps (bounded like every other wait)
-    auto stage_sync = [&]() -> bool {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[L::bStage]);
-      const bool good = mbar_wait(&bars[L::bStage], sph & 1u, abort_flag, status, 0x1D00);
-      ++sph;
-      return good;
-    };
     for (int w = blockIdx.x; ok && w < nitems; w = next_item(drawn++, true)) {
       const DkdvItem it = dkdv_item(p, w);
       if (!it.valid) continue;
@@ -610,38 +601,33 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       if (!mbar_wait(&bars[L::bAccDone], live & 1u, abort_flag, status, 0x1A00)) { ok = false; break; }
       if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G - 1, 13);
       ++live;
-      {
-        // Rows go through a staging tile so that the global stores are whole rows per warp.
+      if (wg < HD / 32) {
+        // Each warp transposes its 32 rows x 32 columns through the staging tile, so that the global
+        // stores are 64-byte row segments instead of 16 bytes per row.
         uint8_t* stage = smem + L::kStage;
-        const int tid = (int)threadIdx.x - 128, nrows = min(kBlk, sq.sk - it.n0);
+        const int nrows = min(kBlk, sq.sk - it.n0);
         const int d0 = wg * 32;
         float v[32];
         tc_fence_after();
-        if (wg < HD / 32) {
-          tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
-          tmem_wait_ld();
-          stage_put32<T>(stage, r, d0, v, 1.0f, HD * 2);
-        }
-        if (!stage_sync()) { ok = false; break; }
-        stage_copy_out<T>(stage, reinterpret_cast<T*>(p.dv.ptr) + (int64_t)sq.bidx * p.dv.s[0] + (int64_t)hk * p.dv.s[1] +
-                                     (sq.k0 + it.n0) * p.dv.s[2],
-                          p.dv.s[2], nrows, p.dvo, tid, kComputeWarps * 32, HD * 2);
-        if (wg < HD / 32) {
-          tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
-          tmem_wait_ld();
-        }
+        tmem_ld32f(tmem_base + lane_addr + kColAcc0 + d0, v);
+        tmem_wait_ld();
+        stage_put32<T>(stage, r, d0, v, 1.0f, HD * 2);
+        __syncwarp();
+        warp_copy_out<T, 4>(stage, reinterpret_cast<T*>(p.dv.ptr) + (int64_t)sq.bidx * p.dv.s[0] + (int64_t)hk * p.dv.s[1] +
+                                       (sq.k0 + it.n0) * p.dv.s[2],
+                            p.dv.s[2], nrows, p.dvo, quarter * 32, wg * 4, lane, HD * 2);
+        tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
+        tmem_wait_ld();
         // The accumulators are in registers now: the next item's first dV/dK GEMMs (which start from
         // zero) are only issued after this thread's next hand-off, i.e. after these loads.
         tc_fence_before();
-        if (!stage_sync()) { ok = false; break; }       // everyone has read dV out of the staging tile
-        if (wg < HD / 32) stage_put32<T>(stage, r, d0, v, p.sm_scale, HD * 2);
-        if (!stage_sync()) { ok = false; break; }
-        stage_copy_out<T>(stage, reinterpret_cast<T*>(p.dk.ptr) + (int64_t)sq.bidx * p.dk.s[0] + (int64_t)hk * p.dk.s[1] +
-                                     (sq.k0 + it.n0) * p.dk.s[2],
-                          p.dk.s[2], nrows, p.dqk, tid, kComputeWarps * 32, HD * 2);
-        if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G - 1, 14);
-        // (the staging tile is next written after this item's successor has had all its hand-offs,
-        // which every warp makes after this point)
+        __syncwarp();
+        stage_put32<T>(stage, r, d0, v, p.sm_scale, HD * 2);
+        __syncwarp();
+        warp_copy_out<T, 4>(stage, reinterpret_cast<T*>(p.dk.ptr) + (int64_t)sq.bidx * p.dk.s[0] + (int64_t)hk * p.dk.s[1] +
+                                       (sq.k0 + it.n0) * p.dk.s[2],
+                            p.dk.s[2], nrows, p.dqk, quarter * 32, wg * 4, lane, HD * 2);
+        __syncwarp();
       }
     }
   }
@@ -666,7 +652,7 @@ struct DqSmem {
   static constexpr int kK = 2 * kTile, kV = kK + kKStages * kTile;
   static constexpr int kBars = kV + kVStages * kTile;
   static constexpr int bResFull = 0, bKFull = 1, bKEmpty = 4, bVFull = 7, bVEmpty = 9, bSFull = 11, bSRead = 12,
-                       bDpFull = 13, bDsFull = 15, bAccDone = 17, bStage = 18, bCount = 19;
+                       bDpFull = 13, bDsFull = 15, bAccDone = 17, bCount = 18;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kDynamic = kAbort + 4 + 1024;
@@ -715,7 +701,6 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     mbar_init(&bars[L::bSFull], 1);
     mbar_init(&bars[L::bSRead], kComputeWarps);
     mbar_init(&bars[L::bAccDone], 1);
-    mbar_init(&bars[L::bStage], kComputeWarps);
     fence_barrier_init();
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
   }
@@ -985,23 +970,20 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 3);
     }
     if (ok) ok = mbar_wait(&bars[L::bAccDone], 0, abort_flag, status, 0x2800);
-    if (ok) {
-      // dQ rows go through the (now idle) Q tile so that the global stores are whole rows per warp
+    if (ok && wg < HD / 32) {
+      // Each warp transposes its 32 rows x 32 columns of dQ through the (now idle) Q tile, so that
+      // the global stores are 64-byte row segments instead of 16 bytes per row.
       uint8_t* stage = smem + L::kResA;
-      if (wg < HD / 32) {
-        tc_fence_after();
-        float v[32];
-        const int d0 = wg * 32;
-        tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
-        tmem_wait_ld();
-        stage_put32<T>(stage, r, d0, v, p.sm_scale, HD * 2);
-      }
+      tc_fence_after();
+      float v[32];
+      const int d0 = wg * 32;
+      tmem_ld32f(tmem_base + lane_addr + kColAcc1 + d0, v);
+      tmem_wait_ld();
+      stage_put32<T>(stage, r, d0, v, p.sm_scale, HD * 2);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[L::bStage]);
-      if (mbar_wait(&bars[L::bStage], 0, abort_flag, status, 0x2900))
-        stage_copy_out<T>(stage, reinterpret_cast<T*>(p.dq.ptr) + (int64_t)sq.bidx * p.dq.s[0] + (int64_t)h * p.dq.s[1] +
+      warp_copy_out<T, 4>(stage, reinterpret_cast<T*>(p.dq.ptr) + (int64_t)sq.bidx * p.dq.s[0] + (int64_t)h * p.dq.s[1] +
                                      (sq.q0 + m0) * p.dq.s[2],
-                          p.dq.s[2], min(kBlk, sq.sq - m0), p.dqk, (int)threadIdx.x - 128, kComputeWarps * 32, HD * 2);
+                          p.dq.s[2], min(kBlk, sq.sq - m0), p.dqk, quarter * 32, wg * 4, lane, HD * 2);
     }
   }
 

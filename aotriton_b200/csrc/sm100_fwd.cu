@@ -78,7 +78,7 @@ struct FwdSmem {
   static constexpr int kBars = kV + kStages * kTileBytes;
   // barrier slots (8 bytes each)
   static constexpr int bQFull = 0 /*2*/, bKFull = 2, bKEmpty = 4, bVFull = 6, bVEmpty = 8, bSFull = 10 /*2*/,
-                       bPFull = 12 /*2*/, bPvDone = 14 /*2*/, bTurn = 16 /*2*/, bStage = 18 /*2*/, bCount = 20;
+                       bPFull = 12 /*2*/, bPvDone = 14 /*2*/, bTurn = 16 /*2*/, bCount = 18;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4;
@@ -149,7 +149,6 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       mbar_init(&bars[L::bPFull + s], 4);      // one arrival per softmax warp of the tile
       mbar_init(&bars[L::bPvDone + s], 1);
       mbar_init(&bars[L::bTurn + s], 4);       // passed on by the four warps of the other tile
-      mbar_init(&bars[L::bStage + s], 4);      // the tile's four warps, before the write-out
     }
     fence_barrier_init();
     prefetch_tmap(&tm_q);
@@ -452,8 +451,8 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
     if (ok) {
       tc_fence_after();
       const float inv = (l > 0.f) ? p.dropout_scale / l : 0.f;
-      // The rows go through the tile's (now idle) Q buffer, so that the global stores are whole
-      // rows per warp instead of 16 bytes per row.
+      // Each warp transposes its 32 rows through the tile's (now idle) Q buffer, so that the global
+      // stores are whole rows instead of 16 bytes per row.
       uint8_t* stage = smem + L::kQ + t * L::kTileBytes;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
@@ -463,11 +462,9 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         stage_put32<T>(stage, r, c * 32, o, inv, HD * 2);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[L::bStage + t]);
-      if (mbar_wait(&bars[L::bStage + t], 0, abort_flag, status, 0xA00 + t))
-        stage_copy_out<T>(stage, reinterpret_cast<T*>(p.out.ptr) + (int64_t)sq.bidx * p.out.s[0] + (int64_t)h * p.out.s[1] +
-                                     (sq.q0 + m0 + t * kBM) * p.out.s[2],
-                          p.out.s[2], min(kBM, sq.sq - (m0 + t * kBM)), p.dvo, (int)threadIdx.x - 128 - t * 128, 128, HD * 2);
+      warp_copy_out<T, HD / 8>(stage, reinterpret_cast<T*>(p.out.ptr) + (int64_t)sq.bidx * p.out.s[0] +
+                                          (int64_t)h * p.out.s[1] + (sq.q0 + m0 + t * kBM) * p.out.s[2],
+                               p.out.s[2], min(kBM, sq.sq - (m0 + t * kBM)), p.dvo, quarter * 32, 0, lane, HD * 2);
       if (p.lse != nullptr && m < sq.sq)
         p.lse[lse_offset(p, sq, h) + m] = (l > 0.f) ? (m_used + log2f(l)) * kLn2 : INFINITY;
     }

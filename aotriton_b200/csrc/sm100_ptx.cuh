@@ -330,10 +330,10 @@ inline EncodeTiledFn tensor_map_encoder() {
   return fn;
 }
 
-// ---- coalesced write-out of a [128 rows x D] 16-bit tile through shared memory -------------
+// ---- write-out of a [128 rows x D] 16-bit tile through shared memory -----------------------
 // A thread that owns one row of a tile (a TMEM lane) would store 16 bytes per instruction at a
 // row stride: 32 separate memory lines per warp instruction, which costs thousands of cycles per
-// tile.  Instead the rows go to a staging tile and are written out with whole rows per warp.
+// tile.  Instead each warp transposes its 32 rows through a staging tile and writes row segments.
 // Staging layout: row r starts at r * row_bytes; 16-byte chunk c of the row sits at position
 // (c & ~7) | ((c ^ r) & 7), which makes both the row-per-thread writes and the chunk-per-thread
 // reads free of bank conflicts.
@@ -353,23 +353,25 @@ __device__ __forceinline__ void stage_put32(uint8_t* stage, int r, int d0, const
     *reinterpret_cast<uint4*>(stage + stage_chunk_offset(r, (d0 >> 3) + v8, row_bytes)) = w;
   }
 }
+// Write-out by the warp that staged them: rows row0..row0+31 of the staging tile, 16-byte chunks
+// c0..c0+nchunks-1 of each row (nchunks = 4: eight rows of 64 bytes per instruction; nchunks =
+// 16: two full rows per instruction).  Only a __syncwarp() separates staging from write-out.
 // `tile` points at row 0 of the tile in global memory (rows `row_stride` elements apart, 16-byte
-// aligned); the first `nrows` rows and `dmax` columns (a multiple of 8) are written.
-template <typename T>
-__device__ __forceinline__ void stage_copy_out(const uint8_t* stage, T* tile, int64_t row_stride, int nrows, int dmax,
-                                               int tid, int nthreads, int row_bytes) {
-  const int cpr = row_bytes >> 4;      // chunks per row: 8 or 16
-  const int shift = (cpr == 16) ? 4 : 3;
-  for (int idx = tid; idx < 128 * cpr; idx += nthreads) {
-    const int r = idx >> shift, c = idx & (cpr - 1);
-    if (r < nrows && c * 8 < dmax)
+// aligned); rows below `nrows` and columns below `dmax` (a multiple of 8) are written.
+template <typename T, int NCHUNKS>
+__device__ __forceinline__ void warp_copy_out(const uint8_t* stage, T* tile, int64_t row_stride, int nrows, int dmax,
+                                              int row0, int c0, int lane, int row_bytes) {
+  constexpr int kRowsPerInstr = 32 / NCHUNKS;
+  const int c = c0 + (lane & (NCHUNKS - 1));
+  const int rl = lane / NCHUNKS;
+  if (c * 8 >= dmax) return;
+#pragma unroll
+  for (int k = 0; k < 32 / kRowsPerInstr; ++k) {
+    const int r = row0 + k * kRowsPerInstr + rl;
+    if (r < nrows)
       *reinterpret_cast<uint4*>(tile + (int64_t)r * row_stride + c * 8) =
           *reinterpret_cast<const uint4*>(stage + stage_chunk_offset(r, c, row_bytes));
   }
-}
-// Barrier among `nthreads` threads (a multiple of 32) of the CTA; id 0 is __syncthreads.
-__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 // Tile map over a (B, H, S, D) view of 16-bit elements: box = 64 columns x `box_rows` rows,
