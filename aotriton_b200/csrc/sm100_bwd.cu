@@ -2,14 +2,19 @@
 // (delta = rowsum(O * dO) is produced beforehand by the streaming preprocess kernel.)
 //
 // Both kernels recompute the probabilities from Q, K and the forward's logsumexp and share
-// one scheme.  A CTA owns 128 rows of its output (keys for dK/dV, queries for dQ) and walks
-// 128-wide blocks of the other sequence dimension.  Twenty warps:
+// one scheme.  A unit of work is 128 rows of the output (keys for dK/dV, queries for dQ) against
+// all reachable 128-wide blocks of the other sequence dimension.  The dQ kernel runs one CTA per
+// unit; the dK/dV kernel is persistent (one CTA per SM draws units from a ticket counter and keeps
+// its pipeline up across them).  Twenty warps:
 //
-//   warp 0      TMA producer   resident operand pair once, then the streamed pair through a
-//                              2-stage ring (cp.async.bulk.tensor, 128-byte swizzle)
-//   warp 1      MMA issuer     one thread issues all tcgen05.mma and tcgen05.commit
+//   warp 0      TMA producer   resident operand pair per unit, the streamed operands through
+//                              rings (cp.async.bulk.tensor, 128-byte swizzle): Q and dO together
+//                              in two stages (dK/dV); K in three stages, V in two (dQ)
+//   warp 1      MMA issuer     walks its loop warp-uniformly, one elected lane issues all
+//                              tcgen05.mma and tcgen05.commit
 //   warp 2      (dK/dV only)   stages logsumexp*log2(e) and delta of the streamed query
 //                              block in shared memory
+//   warp 3      (dK/dV only)   draws the CTA's next unit from the ticket counter
 //   warps 4-19  compute        thread = one output row of the 128x128 score tile (TMEM lane),
 //                              the four warpgroups split its columns 32 apiece
 //
@@ -19,6 +24,7 @@
 //                               dV += P^T dO_i     dK += dS^T Q_i         (A from TMEM)
 //   dQ, per key block i:        S = Q K_i^T        dP = dO V_i^T
 //                               dQ += dS K_i       dB = dS
+//                               (dP runs two blocks ahead in two buffers, S one and a half)
 //
 // Tensor memory, dK/dV: [0,128) S^T, [128,256) dP^T then P^T and dS^T, [256,384) dV, [384,512) dK.
 // Tensor memory, dQ:    [0,128) S, [128,256) and [256,384) two dP / dS buffers, [384,512) dQ.

@@ -6,14 +6,15 @@
 //
 //   warp 0       TMA producer   both Q tiles once, then K and V blocks through two 2-stage rings
 //                               (cp.async.bulk.tensor, 128-byte swizzle, this CTA only)
-//   warp 1       MMA issuer     one elected thread issues, per tile,  S = Q K^T  (operands in
+//   warp 1       MMA issuer     walks its loop warp-uniformly; one elected lane issues, per tile,  S = Q K^T  (operands in
 //                               shared memory) and  O += P V  (P read straight from tensor
 //                               memory, V from shared memory, N-major); completion is signalled
 //                               with tcgen05.commit
 //   warps 4-7    softmax, tile 0        thread r owns query row r of its tile: tcgen05.ld of the S
 //   warps 8-11   softmax, tile 1        row, scale, bias, mask, running max / sum in the exp2
 //                               domain, dropout, P written back over S as packed 16-bit, lazy
-//                               rescale of O, final normalisation, O and LSE stores
+//                               rescale of O, final normalisation, O (transposed per warp
+//                               through the idle Q buffer, whole rows per store) and LSE stores
 //
 // While one tile's softmax warps work on block j, the tensor core runs the other tile's PV and
 // QK^T: the two tiles ping-pong.  The producer and issuer warps give most of their registers

@@ -254,6 +254,11 @@ def main():
     tfl = lambda f, ms: f / (ms * 1e-3) / 1e12
     value = world * tfl(ffwd + fbwd, ms_step)
     dom = max(("attn_fwd", "bwd_dkdv", "bwd_dq"), key=lambda n: kern_ms[n])
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture at batch 2
+    # (profiles/tcgen05_kernels_dense_causal_bf16_B2_H32_S4096_D128.md); traffic grows in
+    # proportion to the batch (per-(batch, head) work is independent), so it is scaled by B / 2.
+    traffic_b2 = {"attn_fwd": 201.6e6 + 54.0e6, "bwd_dkdv": 275.0e6 + 117.5e6, "bwd_dq": 270.6e6 + 55.7e6}
+    dom_traffic = traffic_b2[dom] * B / 2.0 if (H, S, D) == (32, 4096, 128) else None
     dom_flops = {"attn_fwd": ffwd, "bwd_dkdv": 2.0 * ffwd, "bwd_dq": 1.5 * ffwd}[dom]
     nbytes = q.numel() * 2
     line = dict(
@@ -268,10 +273,16 @@ def main():
                      fwd_frac_of_peak=tfl(ffwd, kern_ms["attn_fwd"]) / peaks["bf16"],
                      bwd_frac_of_peak=tfl(fbwd, kern_ms["bwd_preprocess"] + kern_ms["bwd_dkdv"] + kern_ms["bwd_dq"])
                      / peaks["bf16"], kernel_ms=kern_ms,
+                     # the timed loop runs for hundreds of milliseconds under the power cap: the
+                     # cuBLAS figure measured the same way (seconds-long loop) is the fair yardstick
+                     step_tflops=tfl(ffwd + fbwd, ms_step), bf16_peak_sustained=peaks["bf16_sustained"],
+                     step_frac_of_sustained_peak=(tfl(ffwd + fbwd, ms_step) / peaks["bf16_sustained"]
+                                                  if peaks["bf16_sustained"] else None),
                      fwd_family=cabi.lib().ab200_last_fwd_family(), bwd_family=cabi.lib().ab200_last_bwd_family(),
                      preprocess_gbs=(2 * nbytes + lse.numel() * 4) / (kern_ms["bwd_preprocess"] * 1e-3) / 1e9),
         roofline=dict(bound="tensor", kernel=dom, achieved=tfl(dom_flops, kern_ms[dom]), peak=peaks["bf16"],
-                      unit="TFLOP/s", frac=tfl(dom_flops, kern_ms[dom]) / peaks["bf16"], traffic=None,
+                      unit="TFLOP/s", frac=tfl(dom_flops, kern_ms[dom]) / peaks["bf16"], traffic=dom_traffic,
+                      traffic_unit="bytes per launch (ncu at batch 2, scaled by batch)",
                       peak_source=f"of {peaks['src']} (cuBLAS bf16 burst)",
                       flops_note="algorithmic: fwd 4BHS^2D/2; dK/dV 4 of the 5 counted backward GEMMs = 2x fwd; "
                                  "dQ 3 GEMMs = 1.5x fwd (two of them recomputed, counted here because this "
