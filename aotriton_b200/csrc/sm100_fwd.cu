@@ -6,10 +6,11 @@
 //
 //   warp 0       TMA producer   both Q tiles once, then K and V blocks through two 2-stage rings
 //                               (cp.async.bulk.tensor, 128-byte swizzle, this CTA only)
-//   warp 1       MMA issuer     walks its loop warp-uniformly; one elected lane issues, per tile,  S = Q K^T  (operands in
-//                               shared memory) and  O += P V  (P read straight from tensor
+//   warp 1       MMA issuer     walks its loop warp-uniformly; one elected lane issues, per
+//                               tile,  S = Q K^T  (operands in shared memory) and  O += P V  (P read straight from tensor
 //                               memory, V from shared memory, N-major); completion is signalled
-//                               with tcgen05.commit
+//                               with tcgen05.commit.  P arrives in two halves of 64 keys, so
+//                               the first half of P V runs under the second half's exponentials
 //   warps 4-7    softmax, tile 0        thread r owns query row r of its tile: tcgen05.ld of the S
 //   warps 8-11   softmax, tile 1        row, scale, bias, mask, running max / sum in the exp2
 //                               domain, dropout, P written back over S as packed 16-bit, lazy
@@ -79,7 +80,7 @@ struct FwdSmem {
   static constexpr int kBars = kV + kStages * kTileBytes;
   // barrier slots (8 bytes each)
   static constexpr int bQFull = 0 /*2*/, bKFull = 2, bKEmpty = 4, bVFull = 6, bVEmpty = 8, bSFull = 10 /*2*/,
-                       bPFull = 12 /*2*/, bPvDone = 14 /*2*/, bTurn = 16 /*2*/, bCount = 18;
+                       bPFull = 12 /*2*/, bPvDone = 14 /*2*/, bTurn = 16 /*2*/, bPHalf = 18 /*2*/, bCount = 20;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4;
@@ -150,6 +151,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       mbar_init(&bars[L::bPFull + s], 4);      // one arrival per softmax warp of the tile
       mbar_init(&bars[L::bPvDone + s], 1);
       mbar_init(&bars[L::bTurn + s], 4);       // passed on by the four warps of the other tile
+      mbar_init(&bars[L::bPHalf + s], 4);      // first 64 keys of P written
     }
     fence_barrier_init();
     prefetch_tmap(&tm_q);
@@ -253,16 +255,26 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         const uint64_t vd = v_desc + (uint64_t)((uint32_t)s * kStageStep);
         const uint32_t first = (j > 0) ? 1u : 0u;
         for (int t = 0; ok && t < ntile; ++t) {
-          if (!wait(L::bPFull + t, par, 0x500 + 2 * j + t)) { ok = false; break; }
-          tc_fence_after();
+          // P arrives in two halves of 64 keys: the first half of P V runs while the softmax warps
+          // are still working on the second.
           const uint32_t pcol = tmem_base + (uint32_t)t * 128u;
           const uint32_t ocol = tmem_base + 256u + (uint32_t)t * 128u;
+          if (!wait(L::bPHalf + t, par, 0x580 + 2 * j + t)) { ok = false; break; }
+          tc_fence_after();
           if (elect_one()) {
 #pragma unroll
-            for (int kk = 0; kk < kBN / 16; ++kk) {
+            for (int kk = 0; kk < kBN / 32; ++kk) {
               // 16 keys per step: 8 packed columns of P, 2048 bytes of V (two 8-key groups)
               mma_ts(ocol, pcol + (uint32_t)kk * 8u, vd + (uint32_t)kk * (2048u >> 4), kIdescPV, kk > 0 ? 1u : first);
             }
+          }
+          __syncwarp();
+          if (!wait(L::bPFull + t, par, 0x500 + 2 * j + t)) { ok = false; break; }
+          tc_fence_after();
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = kBN / 32; kk < kBN / 16; ++kk)
+              mma_ts(ocol, pcol + (uint32_t)kk * 8u, vd + (uint32_t)kk * (2048u >> 4), kIdescPV, 1u);
             mma_commit(&bars[L::bPvDone + t]);
             if (t == ntile - 1) mma_commit(&bars[L::bVEmpty + s]);
           }
@@ -395,46 +407,59 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       float2 s4[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) s4[c] = make_float2(0.f, 0.f);
-      if (simple) {
-        const float2 sc2 = make_float2(p.qk_scale, p.qk_scale), nm2 = make_float2(-m_safe, -m_safe);
+      // Exponentials, dropout and the packed P in two halves of 64 keys; the first half is handed
+      // to the MMA issuer while the second is being computed.
 #pragma unroll
-        for (int c = 0; c < 128; c += 2) {
-          const float2 a = fma2(make_float2(sc[c], sc[c + 1]), sc2, nm2);
-          sc[c] = ex2(a.x);
-          sc[c + 1] = ex2(a.y);
-          s4[(c >> 1) & 3] = add2(s4[(c >> 1) & 3], make_float2(sc[c], sc[c + 1]));
+      for (int half = 0; half < 2; ++half) {
+        const int cb = half * 64;
+        if (simple) {
+          const float2 sc2 = make_float2(p.qk_scale, p.qk_scale), nm2 = make_float2(-m_safe, -m_safe);
+#pragma unroll
+          for (int c = cb; c < cb + 64; c += 2) {
+            const float2 a = fma2(make_float2(sc[c], sc[c + 1]), sc2, nm2);
+            sc[c] = ex2(a.x);
+            sc[c + 1] = ex2(a.y);
+            s4[(c >> 1) & 3] = add2(s4[(c >> 1) & 3], make_float2(sc[c], sc[c + 1]));
+          }
+        } else {
+          const float2 nm2 = make_float2(-m_safe, -m_safe);
+#pragma unroll
+          for (int c = cb; c < cb + 64; c += 2) {
+            const float2 a = add2(make_float2(sc[c], sc[c + 1]), nm2);
+            sc[c] = ex2(a.x);
+            sc[c + 1] = ex2(a.y);
+            s4[(c >> 1) & 3] = add2(s4[(c >> 1) & 3], make_float2(sc[c], sc[c + 1]));
+          }
         }
-      } else {
-        const float2 nm2 = make_float2(-m_safe, -m_safe);
+        // (the row sum uses the values before dropout: it was accumulated above)
+        if (p.dropout_on) {
+          const int mm = min(m, p.max_sq - 1);
 #pragma unroll
-        for (int c = 0; c < 128; c += 2) {
-          const float2 a = add2(make_float2(sc[c], sc[c + 1]), nm2);
-          sc[c] = ex2(a.x);
-          sc[c + 1] = ex2(a.y);
-          s4[(c >> 1) & 3] = add2(s4[(c >> 1) & 3], make_float2(sc[c], sc[c + 1]));
+          for (int c4 = half * 16; c4 < half * 16 + 16; ++c4) {
+            const uint32_t keep = dropout_keep4(dctx, mm, (n0 >> 2) + c4);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (!((keep >> i) & 1u)) sc[c4 * 4 + i] = 0.f;
+          }
+        }
+        // P over the first 64 columns of this S buffer, two 16-bit values per column.
+#pragma unroll
+        for (int c = half * 2; c < half * 2 + 2; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(sc[c * 32 + 2 * i], sc[c * 32 + 2 * i + 1]);
+          tmem_st16(s_addr + c * 16, pk);
+        }
+        if (half == 0) {
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[L::bPHalf + t]);
+          AB200_FSTAMP(j, 4);
         }
       }
       const float sum = ((s4[0].x + s4[0].y) + (s4[1].x + s4[1].y)) + ((s4[2].x + s4[2].y) + (s4[3].x + s4[3].y));
       l += sum;
-      AB200_FSTAMP(j, 4);
-      if (p.dropout_on) {
-        const int mm = min(m, p.max_sq - 1);
-#pragma unroll
-        for (int c4 = 0; c4 < 32; ++c4) {
-          const uint32_t keep = dropout_keep4(dctx, mm, (n0 >> 2) + c4);
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            if (!((keep >> i) & 1u)) sc[c4 * 4 + i] = 0.f;
-        }
-      }
-      // P over the first 64 columns of this S buffer, two 16-bit values per column.
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(sc[c * 32 + 2 * i], sc[c * 32 + 2 * i + 1]);
-        tmem_st16(s_addr + c * 16, pk);
-      }
       AB200_FSTAMP(j, 5);
       tmem_wait_st();
       tc_fence_before();
