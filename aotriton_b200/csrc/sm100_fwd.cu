@@ -65,10 +65,6 @@ constexpr int kCtaRows = 2 * kBM;
 constexpr int kFwdThreads = 384;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;
-// Strict alternation of the two tiles' softmax (tile 0 block j, tile 1 block j, ...).  Measured
-// slower than letting the warpgroups overlap freely (0.87 ms vs 0.70 ms on the benchmark), because
-// one softmax warp per scheduler cannot keep the FMA, ALU and special-function pipes busy at once.
-constexpr bool kTakeTurns = false;
 
 template <int HD>
 struct FwdSmem {
@@ -80,7 +76,7 @@ struct FwdSmem {
   static constexpr int kBars = kV + kStages * kTileBytes;
   // barrier slots (8 bytes each)
   static constexpr int bQFull = 0 /*2*/, bKFull = 2, bKEmpty = 4, bVFull = 6, bVEmpty = 8, bSFull = 10 /*2*/,
-                       bPFull = 12 /*2*/, bPvDone = 14 /*2*/, bTurn = 16 /*2*/, bPHalf = 18 /*2*/, bCount = 20;
+                       bPFull = 12 /*2*/, bPvDone = 14 /*2*/, bPHalf = 16 /*2*/, bCount = 18;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4;
@@ -150,7 +146,6 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       mbar_init(&bars[L::bSFull + s], 1);
       mbar_init(&bars[L::bPFull + s], 4);      // one arrival per softmax warp of the tile
       mbar_init(&bars[L::bPvDone + s], 1);
-      mbar_init(&bars[L::bTurn + s], 4);       // passed on by the four warps of the other tile
       mbar_init(&bars[L::bPHalf + s], 4);      // first 64 keys of P written
     }
     fence_barrier_init();
@@ -315,12 +310,6 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       const int n0 = (jb_lo + j) * kBN;
       const uint32_t par = (uint32_t)j & 1u;
       if (!mbar_wait(&bars[L::bSFull + t], par, abort_flag, status, 0x700 + 2 * j + t)) { ok = false; break; }
-      // Optional strict ping-pong between the two tiles (see kTakeTurns).
-      if (kTakeTurns && ntile == 2 &&
-          !mbar_wait(&bars[L::bTurn + t], t == 0 ? (par ^ 1u) : par, abort_flag, status, 0xA00 + 2 * j + t)) {
-        ok = false;
-        break;
-      }
       AB200_FSTAMP(j, 0);
       tc_fence_after();
       float sc[128];
@@ -464,10 +453,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&bars[L::bPFull + t]);
-        if (kTakeTurns && ntile == 2) mbar_arrive(&bars[L::bTurn + (t ^ 1)]);
-      }
+      if (lane == 0) mbar_arrive(&bars[L::bPFull + t]);
       AB200_FSTAMP(j, 6);
     }
     // ---- epilogue ---------------------------------------------------------------------

@@ -87,6 +87,10 @@ CASES = [
     (torch.float16, 1, 2, 2, 300, 300, 128, 128, (3, 5, 7), 0.1, False),
     (torch.bfloat16, 1, 1, 1, 1, 1, 128, 128, (3, TL, TL), 0.0, False),
     (torch.float16, 1, 3, 3, 129, 1, 32, 32, (0, 0, 0), 0.0, False),
+    # a whole 128-row tile of dead rows beside a live one (bottom-right causal, Sq > Sk)
+    (torch.bfloat16, 1, 2, 2, 300, 100, 128, 128, (3, BR, BR), 0.0, False),
+    # sliding window over several key blocks: the two query tiles of a CTA reach different blocks
+    (torch.float16, 1, 2, 1, 700, 700, 64, 64, (3, 130, 20), 0.0, False),
 ]
 
 
