@@ -99,7 +99,7 @@ struct BwdSmem {
   static constexpr int kAuxFlag = kAux + 2 * 256 * 4;    // per stage: 1 when some |lse2| is huge
   static constexpr int kSched = kAuxFlag + 16;             // two slots: next work item of this CTA
   static constexpr int kBars = kSched + 16;
-  static constexpr int bResFull = 0, bRingFull = 1, bRingEmpty = 3, bAuxFull = 5, bAuxEmpty = 7, bSFull = 9,
+  static constexpr int bResFull = 0, bRingFull = 1, bRingEmpty = 3, bSFull = 5 /* two */, bAuxEmpty = 7,
                        bDpFull = 10 /* two: one per dP buffer in the dQ kernel */, bDsFull = 12, bAccDone = 13, bSRead = 14,
                        bResEmpty = 15, bPFull = 16, bSchedFull = 17, bSchedEmpty = 19,
                        bCount = 21;
@@ -158,12 +158,11 @@ __device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t*
   for (int s = 0; s < 2; ++s) {
     mbar_init(&bars[L::bRingFull + s], 1);
     mbar_init(&bars[L::bRingEmpty + s], 1);
-    mbar_init(&bars[L::bAuxFull + s], 1);
+    mbar_init(&bars[L::bSFull + s], 2);          // the S GEMM's commit and the aux warp's arrival
     mbar_init(&bars[L::bAuxEmpty + s], kComputeWarps);
     mbar_init(&bars[L::bSchedFull + s], 1);
     mbar_init(&bars[L::bSchedEmpty + s], kComputeWarps + 3);   // compute warps, producer, MMA issuer, aux warp
   }
-  mbar_init(&bars[L::bSFull], 1);
   mbar_init(&bars[L::bDpFull], 1);
   mbar_init(&bars[L::bDpFull + 1], 1);
   mbar_init(&bars[L::bDsFull], kComputeWarps);
@@ -225,6 +224,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kTmemSlot);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAbort);
   float* aux = reinterpret_cast<float*>(smem + L::kAux);
+  const uint32_t aux_s = smem_u32(smem + L::kAux);
   volatile uint32_t* aux_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAuxFlag);
   volatile int* sched = reinterpret_cast<volatile int*>(smem + L::kSched);
 
@@ -280,10 +280,11 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           tma_load_4d(smem + L::kResA + hf * 16384, &tm_k, &bars[L::bResFull], hf * 64, krow, it.hk, it.sq.bidx);
           tma_load_4d(smem + L::kResB + hf * 16384, &tm_v, &bars[L::bResFull], hf * 64, krow, it.hk, it.sq.bidx);
         }
-        for (int i = 0; i < it.niter; ++i, ++G) {
+        for (int i = 0, hg = 0, mb = 0; i < it.niter; ++i, ++G) {     // hg, mb: i / nmb, i % nmb
           const int s = (int)(G & 1u);
-          const int h = it.hk * p.group + i / it.nmb;
-          const int mrow = (int)(it.sq.q0 + (int64_t)(it.mb_lo + i % it.nmb) * kBlk);
+          const int h = it.hk * p.group + hg;
+          const int mrow = (int)(it.sq.q0 + (int64_t)(it.mb_lo + mb) * kBlk);
+          if (++mb == it.nmb) { mb = 0; ++hg; }
           if (!mbar_wait(&bars[L::bRingEmpty + s], ((G >> 1) & 1u) ^ 1u, abort_flag, status, 0x1100)) { ok = false; break; }
           mbar_expect_tx(&bars[L::bRingFull + s], 2 * L::kTile);
           for (int hf = 0; hf < L::kHalves; ++hf) {
@@ -321,7 +322,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
           mma_ss(tmem_base + kColS, k_km + kmajor_step(kk), qa + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
-        mma_commit(&bars[L::bSFull]);
+        mma_commit(&bars[L::bSFull + (g & 1u)]);
       }
       __syncwarp();
     };
@@ -398,11 +399,12 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     for (int w = blockIdx.x; ok && w < nitems; w = next_item(drawn++, true)) {
       const DkdvItem it = dkdv_item(p, w);
       if (!it.valid || it.niter == 0) continue;
-      for (int i = 0; i < it.niter; ++i, ++G) {
+      for (int i = 0, hg = 0, mb = 0; i < it.niter; ++i, ++G) {     // hg, mb: i / nmb, i % nmb
         const int s = (int)(G & 1u);
-        if (!mbar_wait(&bars[L::bAuxEmpty + s], ((G >> 1) & 1u) ^ 1u, abort_flag, status, 0x1600)) { ok = false; break; }
-        const int h = it.hk * p.group + i / it.nmb;
-        const int mbase = (it.mb_lo + i % it.nmb) * kBlk;
+        if (!mbar_wait_relaxed(&bars[L::bAuxEmpty + s], ((G >> 1) & 1u) ^ 1u, abort_flag, status, 0x1600)) { ok = false; break; }
+        const int h = it.hk * p.group + hg;
+        const int mbase = (it.mb_lo + mb) * kBlk;
+        if (++mb == it.nmb) { mb = 0; ++hg; }
         const int64_t lrow = lse_offset(p, it.sq, h);
         float* dst = aux + s * 256;
         bool huge = false;
@@ -424,7 +426,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         const bool any_huge = __any_sync(0xffffffffu, huge);
         if (lane == 0) aux_flag[s] = any_huge ? 1u : 0u;
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[L::bAuxFull + s]);
+        if (lane == 0) mbar_arrive(&bars[L::bSFull + s]);
       }
     }
   } else if (warp == 3) {
@@ -432,7 +434,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     if (lane == 0) {
       for (uint32_t m = 0;; ++m) {
         const uint32_t k = m & 1u;
-        if (!mbar_wait(&bars[L::bSchedEmpty + k], ((m >> 1) & 1u) ^ 1u, abort_flag, status, 0x1C00)) break;
+        if (!mbar_wait_relaxed(&bars[L::bSchedEmpty + k], ((m >> 1) & 1u) ^ 1u, abort_flag, status, 0x1C00)) break;
         const unsigned int t = atomicAdd(ticket, 1u);
         const int w = t < 0x40000000u ? (int)(gridDim.x + t) : 0x7fffffff;
         sched[k] = w;
@@ -474,16 +476,17 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         if (hi < col_hi) col_hi = (int)(hi < -1 ? -1 : hi);
       }
       if (n >= sq.sk) { col_lo = 1; col_hi = 0; }
-      for (int i = 0; i < it.niter; ++i, ++G) {
+      for (int i = 0, hg = 0, mb = 0; i < it.niter; ++i, ++G) {     // hg, mb: i / nmb, i % nmb
         const int s = (int)(G & 1u);
         const uint32_t par = G & 1u;
-        const int h = hk * p.group + i / it.nmb;
-        const int mbase = (it.mb_lo + i % it.nmb) * kBlk + cbase;    // first query row of this thread's columns
-        const float* lse2 = aux + s * 256 + cbase;
-        const float* dlt = lse2 + 128;
-        if (!mbar_wait(&bars[L::bAuxFull + s], (G >> 1) & 1u, abort_flag, status, 0x1700)) { ok = false; break; }
+        const int h = hk * p.group + hg;
+        const int mbase = (it.mb_lo + mb) * kBlk + cbase;    // first query row of this thread's columns
+        if (++mb == it.nmb) { mb = 0; ++hg; }
+        const uint32_t lse2 = aux_s + (uint32_t)(s * 256 + cbase) * 4u;      // shared-space addresses
+        const uint32_t dlt = lse2 + 128u * 4u;
         if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 4);
-        if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x1800)) { ok = false; break; }
+        // S^T of this block and its logsumexp/delta stage (two arrivals on one barrier)
+        if (!mbar_wait(&bars[L::bSFull + s], (G >> 1) & 1u, abort_flag, status, 0x1800)) { ok = false; break; }
         if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 0);
         tc_fence_after();
         float pr[32];
@@ -503,7 +506,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           const float2 sc2 = make_float2(p.qk_scale, p.qk_scale);
 #pragma unroll
           for (int c4 = 0; c4 < 8; ++c4) {
-            const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
+            const float4 l4 = lds128(lse2 + 16u * c4);
             const float2 a = fma2(make_float2(pr[4 * c4], pr[4 * c4 + 1]), sc2, make_float2(-l4.x, -l4.y));
             const float2 b = fma2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]), sc2, make_float2(-l4.z, -l4.w));
             pr[4 * c4 + 0] = ex2(a.x);
@@ -526,7 +529,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           __syncwarp();   // lanes beyond the sequence skipped the loads
 #pragma unroll
           for (int c4 = 0; c4 < 8; ++c4) {
-            const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
+            const float4 l4 = lds128(lse2 + 16u * c4);
             pr[4 * c4 + 0] = ex2(pr[4 * c4 + 0] - l4.x);
             pr[4 * c4 + 1] = ex2(pr[4 * c4 + 1] - l4.y);
             pr[4 * c4 + 2] = ex2(pr[4 * c4 + 2] - l4.z);
@@ -582,7 +585,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           }
 #pragma unroll
           for (int c4 = 0; c4 < 8; ++c4) {
-            const float4 d4 = *reinterpret_cast<const float4*>(dlt + 4 * c4);
+            const float4 d4 = lds128(dlt + 16u * c4);
             const float2 a = mul2(make_float2(pr[4 * c4], pr[4 * c4 + 1]),
                                   sub2(make_float2(dp[4 * c4], dp[4 * c4 + 1]), make_float2(d4.x, d4.y)));
             const float2 b = mul2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]),
