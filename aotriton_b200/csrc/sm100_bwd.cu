@@ -12,7 +12,7 @@
 //                              in two stages (dK/dV); K in three stages, V in two (dQ)
 //   warp 1      MMA issuer     walks its loop warp-uniformly, one elected lane issues all
 //                              tcgen05.mma and tcgen05.commit
-//   warp 2      (dK/dV only)   stages logsumexp*log2(e) and delta of the streamed query
+//   warp 2      (dK/dV only)   stages -logsumexp*log2(e) and -delta of the streamed query
 //                              block in shared memory
 //   warp 3      (dK/dV only)   draws the CTA's next unit from the ticket counter
 //   warps 4-19  compute        thread = one output row of the 128x128 score tile (TMEM lane),
@@ -421,8 +421,10 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           l2[t] *= kLog2e;
           huge = huge || (fabsf(l2[t]) > 1.0e6f && l2[t] != INFINITY);
         }
-        *reinterpret_cast<float4*>(dst + lane * 4) = make_float4(l2[0], l2[1], l2[2], l2[3]);
-        *reinterpret_cast<float4*>(dst + 128 + lane * 4) = make_float4(dl[0], dl[1], dl[2], dl[3]);
+        // staged NEGATED (-logsumexp*log2e, -delta): the compute warps add them with packed
+        // instructions, which take no negate modifier
+        *reinterpret_cast<float4*>(dst + lane * 4) = make_float4(-l2[0], -l2[1], -l2[2], -l2[3]);
+        *reinterpret_cast<float4*>(dst + 128 + lane * 4) = make_float4(-dl[0], -dl[1], -dl[2], -dl[3]);
         const bool any_huge = __any_sync(0xffffffffu, huge);
         if (lane == 0) aux_flag[s] = any_huge ? 1u : 0u;
         __syncwarp();
@@ -507,8 +509,8 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
 #pragma unroll
           for (int c4 = 0; c4 < 8; ++c4) {
             const float4 l4 = lds128(lse2 + 16u * c4);
-            const float2 a = fma2(make_float2(pr[4 * c4], pr[4 * c4 + 1]), sc2, make_float2(-l4.x, -l4.y));
-            const float2 b = fma2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]), sc2, make_float2(-l4.z, -l4.w));
+            const float2 a = fma2(make_float2(pr[4 * c4], pr[4 * c4 + 1]), sc2, make_float2(l4.x, l4.y));
+            const float2 b = fma2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]), sc2, make_float2(l4.z, l4.w));
             pr[4 * c4 + 0] = ex2(a.x);
             pr[4 * c4 + 1] = ex2(a.y);
             pr[4 * c4 + 2] = ex2(b.x);
@@ -530,10 +532,10 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
 #pragma unroll
           for (int c4 = 0; c4 < 8; ++c4) {
             const float4 l4 = lds128(lse2 + 16u * c4);
-            pr[4 * c4 + 0] = ex2(pr[4 * c4 + 0] - l4.x);
-            pr[4 * c4 + 1] = ex2(pr[4 * c4 + 1] - l4.y);
-            pr[4 * c4 + 2] = ex2(pr[4 * c4 + 2] - l4.z);
-            pr[4 * c4 + 3] = ex2(pr[4 * c4 + 3] - l4.w);
+            pr[4 * c4 + 0] = ex2(pr[4 * c4 + 0] + l4.x);
+            pr[4 * c4 + 1] = ex2(pr[4 * c4 + 1] + l4.y);
+            pr[4 * c4 + 2] = ex2(pr[4 * c4 + 2] + l4.z);
+            pr[4 * c4 + 3] = ex2(pr[4 * c4 + 3] + l4.w);
           }
         }
         if (any_mask) {
@@ -587,9 +589,9 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           for (int c4 = 0; c4 < 8; ++c4) {
             const float4 d4 = lds128(dlt + 16u * c4);
             const float2 a = mul2(make_float2(pr[4 * c4], pr[4 * c4 + 1]),
-                                  sub2(make_float2(dp[4 * c4], dp[4 * c4 + 1]), make_float2(d4.x, d4.y)));
+                                  add2(make_float2(dp[4 * c4], dp[4 * c4 + 1]), make_float2(d4.x, d4.y)));
             const float2 b = mul2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]),
-                                  sub2(make_float2(dp[4 * c4 + 2], dp[4 * c4 + 3]), make_float2(d4.z, d4.w)));
+                                  add2(make_float2(dp[4 * c4 + 2], dp[4 * c4 + 3]), make_float2(d4.z, d4.w)));
             pk[2 * c4] = pack2<T>(a.x, a.y);
             pk[2 * c4 + 1] = pack2<T>(b.x, b.y);
           }
