@@ -2,8 +2,8 @@
 
 Runs the UNMODIFIED Triton kernels of ROCm/aotriton (modules/flash/kernel/fwd_kernel.py,
 bwd_preprocess.py, bwd_kernel_dk_dv.py, bwd_kernel_dq.py, dropout.py) on CPU tensors with the
-Triton interpreter (TRITON_INTERPRET=1) and stores inputs and outputs as .npz files.  Needs the
-reference checkout (default /root/reference, override with AOTRITON_REFERENCE) and triton; the
+Triton interpreter (TRITON_INTERPRET=1) and stores inputs and outputs as .npz files.  Needs a
+checkout of ROCm/aotriton (its path in AOTRITON_REFERENCE) and triton; the
 test-suite only reads the committed .npz files and never runs this script.
 
 Two harness-side shims, neither touching the reference sources:
@@ -13,7 +13,7 @@ Two harness-side shims, neither touching the reference sources:
     no `.to`), so dropout is pinned through `fast_dropout_mask`, the function every kernel calls
     for its keep bits, wrapped in a six-line kernel that loads seed/base/threshold from tensors.
 
-Usage: python tests/golden/make_golden.py
+Usage: AOTRITON_REFERENCE=<checkout> python tests/golden/make_golden.py
 """
 import builtins
 import math
@@ -22,7 +22,9 @@ import sys
 
 os.environ["TRITON_INTERPRET"] = "1"
 os.environ["TRITON_F32_DEFAULT"] = "ieee"
-REF = os.environ.get("AOTRITON_REFERENCE", "/root/reference")
+REF = os.environ.get("AOTRITON_REFERENCE")
+if not REF:
+    sys.exit("set AOTRITON_REFERENCE to a checkout of ROCm/aotriton")
 sys.path.insert(0, os.path.join(REF, "modules/flash/kernel"))
 
 import numpy as np
