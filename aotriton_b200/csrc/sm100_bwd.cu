@@ -713,7 +713,24 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     mbar_init(&bars[L::bSRead], kComputeWarps);
     mbar_init(&bars[L::bAccDone], 1);
     fence_barrier_init();
-    prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
+    // This thread is also the TMA producer: Q, dO and the first two K and V blocks (all ring stages
+    // are free) are requested right away, before the CTA-wide synchronisation and the tensor-memory
+    // allocation, which then overlap with the copies' latency.
+    const int qrow = (int)(sq.q0 + m0);
+    mbar_expect_tx(&bars[L::bResFull], 2 * L::kTile);
+    for (int hf = 0; hf < L::kHalves; ++hf) {
+      tma_load_4d(smem + L::kResA + hf * 16384, &tm_q, &bars[L::bResFull], hf * 64, qrow, h, sq.bidx);
+      tma_load_4d(smem + L::kResB + hf * 16384, &tm_do, &bars[L::bResFull], hf * 64, qrow, h, sq.bidx);
+    }
+    for (int i = 0; i < min(2, niter); ++i) {
+      const int krow = (int)(sq.k0 + (int64_t)(jb_lo + i) * kBlk);
+      mbar_expect_tx(&bars[L::bKFull + i], L::kTile);
+      for (int hf = 0; hf < L::kHalves; ++hf)
+        tma_load_4d(smem + L::kK + i * L::kTile + hf * 16384, &tm_k, &bars[L::bKFull + i], hf * 64, krow, hk, sq.bidx);
+      mbar_expect_tx(&bars[L::bVFull + i], L::kTile);
+      for (int hf = 0; hf < L::kHalves; ++hf)
+        tma_load_4d(smem + L::kV + i * L::kTile + hf * 16384, &tm_v, &bars[L::bVFull + i], hf * 64, krow, hk, sq.bidx);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -726,14 +743,9 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
 
   if (warp == 0) {
     if (lane == 0) {
-      const int qrow = (int)(sq.q0 + m0);
-      mbar_expect_tx(&bars[L::bResFull], 2 * L::kTile);
-      for (int hf = 0; hf < L::kHalves; ++hf) {
-        tma_load_4d(smem + L::kResA + hf * 16384, &tm_q, &bars[L::bResFull], hf * 64, qrow, h, sq.bidx);
-        tma_load_4d(smem + L::kResB + hf * 16384, &tm_do, &bars[L::bResFull], hf * 64, qrow, h, sq.bidx);
-      }
-      int issued_k = 0, issued_v = 0;
-      for (int i = 0; i < niter; ++i) {
+      // (Q, dO and the first two K and V blocks were requested during set-up)
+      int issued_k = min(2, niter), issued_v = min(2, niter);
+      for (int i = min(2, niter); i < niter; ++i) {
         const int sv = i & 1, sk = i % L::kKStages;
         const int krow = (int)(sq.k0 + (int64_t)(jb_lo + i) * kBlk);
         if (!mbar_wait(&bars[L::bKEmpty + sk], ((uint32_t)(i / L::kKStages) & 1u) ^ 1u, abort_flag, status, 0x2180 + i)) break;

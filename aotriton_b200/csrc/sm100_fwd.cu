@@ -149,9 +149,24 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       mbar_init(&bars[L::bPHalf + s], 4);      // first 64 keys of P written
     }
     fence_barrier_init();
-    prefetch_tmap(&tm_q);
-    prefetch_tmap(&tm_k);
-    prefetch_tmap(&tm_v);
+    // This thread is also the TMA producer: both Q tiles and the first blocks of K and V (the ring
+    // stages are all free) are requested right away, before the CTA-wide synchronisation and the
+    // tensor-memory allocation, which then overlap with the copies' latency.
+    for (int t = 0; t < ntile; ++t) {
+      const int qrow = (int)(sq.q0 + m0 + t * kBM);
+      mbar_expect_tx(&bars[L::bQFull + t], L::kTileBytes);
+      for (int hf = 0; hf < L::kHalves; ++hf)
+        tma_load_4d(smem + L::kQ + t * L::kTileBytes + hf * 16384, &tm_q, &bars[L::bQFull + t], hf * 64, qrow, h, sq.bidx);
+    }
+    for (int j = 0; j < min(kStages, nblk); ++j) {
+      const int krow = (int)(sq.k0 + (int64_t)(jb_lo + j) * kBN);
+      mbar_expect_tx(&bars[L::bKFull + j], L::kTileBytes);
+      for (int hf = 0; hf < L::kHalves; ++hf)
+        tma_load_4d(smem + L::kK + j * L::kTileBytes + hf * 16384, &tm_k, &bars[L::bKFull + j], hf * 64, krow, hk, sq.bidx);
+      mbar_expect_tx(&bars[L::bVFull + j], L::kTileBytes);
+      for (int hf = 0; hf < L::kHalves; ++hf)
+        tma_load_4d(smem + L::kV + j * L::kTileBytes + hf * 16384, &tm_v, &bars[L::bVFull + j], hf * 64, krow, hk, sq.bidx);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -167,15 +182,9 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
     if (warp == 0) {
       // =============================== TMA producer ===================================
       if (lane == 0) {
-        for (int t = 0; t < ntile; ++t) {
-          const int qrow = (int)(sq.q0 + m0 + t * kBM);
-          mbar_expect_tx(&bars[L::bQFull + t], L::kTileBytes);
-          for (int hf = 0; hf < L::kHalves; ++hf)
-            tma_load_4d(smem + L::kQ + t * L::kTileBytes + hf * 16384, &tm_q, &bars[L::bQFull + t], hf * 64, qrow, h,
-                        sq.bidx);
-        }
-        int issued = 0;
-        for (int j = 0; j < nblk; ++j) {
+        // (the Q tiles and the first kStages blocks were requested during set-up)
+        int issued = 2 * min(kStages, nblk);
+        for (int j = min(kStages, nblk); j < nblk; ++j) {
           const int s = j % kStages;
           const uint32_t ph = (uint32_t)(j / kStages) & 1u;
           const int krow = (int)(sq.k0 + (int64_t)(jb_lo + j) * kBN);
