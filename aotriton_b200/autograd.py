@@ -30,6 +30,17 @@ def _philox_tensors(device, dropout_p, seed, offset1):
     return mk(seed), mk(offset1), DEFAULT_PHILOX_OFFSET_2, mk(0), mk(0)
 
 
+# Kernel family of the most recent backward (the library keeps it per thread, and autograd runs
+# backward on a thread of its own): 1 = general, 2 = tcgen05, 0 = none yet.
+last_bwd_family = 0
+
+
+def _note_bwd_family():
+    global last_bwd_family
+    from . import cabi
+    last_bwd_family = int(cabi.lib().ab200_last_bwd_family())
+
+
 class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, b, causal, sm_scale, dropout_p, return_lse=False,
@@ -55,6 +66,7 @@ class _Attention(torch.autograd.Function):
         delta = torch.empty_like(L)
         _check(flash.attn_bwd(q, k, v, b, ctx.sm_scale, o, do, dq, dk, dv, db, None, L, flash.eager_delta(delta),
                               ctx.dropout_p, ctx.philox_seed, ctx.philox_offset, 0, ctx.causal), "attn_bwd")
+        _note_bwd_family()
         return dq, dk, dv, db, None, None, None, None, None, None
 
 
@@ -95,6 +107,7 @@ class _VarlenAttention(torch.autograd.Function):
                                      ctx.sm_scale, o, do, dq, dk, dv, None, None, L, flash.eager_delta(delta),
                                      ctx.dropout_p, ctx.philox_seed, ctx.philox_offset, 0, ctx.causal,
                                      "compact"), "attn_bwd (varlen)")
+        _note_bwd_family()
         return (dq, dk, dv) + (None,) * 10
 
 
