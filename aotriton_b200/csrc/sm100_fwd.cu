@@ -178,7 +178,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
-    reg_dealloc<40>();
+    reg_dealloc<56>();
     if (warp == 0) {
       // =============================== TMA producer ===================================
       if (lane == 0) {
@@ -290,7 +290,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
     }
   } else {
     // ================================== softmax =====================================
-    reg_alloc<224>();
+    reg_alloc<216>();
     const int t = (warp - 4) >> 2;              // tile of this warpgroup
     if (t < ntile) {
     const int quarter = warp & 3;
