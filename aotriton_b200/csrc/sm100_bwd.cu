@@ -478,6 +478,8 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         if (hi < col_hi) col_hi = (int)(hi < -1 ? -1 : hi);
       }
       if (n >= sq.sk) { col_lo = 1; col_hi = 0; }
+      // the tightest bounds over the warp's rows: a block needs masking iff it is not inside them
+      const int warp_lo = __reduce_max_sync(0xffffffffu, col_lo), warp_hi = __reduce_min_sync(0xffffffffu, col_hi);
       for (int i = 0, hg = 0, mb = 0; i < it.niter; ++i, ++G) {     // hg, mb: i / nmb, i % nmb
         const int s = (int)(G & 1u);
         const uint32_t par = G & 1u;
@@ -498,8 +500,8 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[L::bSRead]);
         if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 6);
-        const bool need_mask = !(mbase >= col_lo && mbase + kWgCols - 1 <= col_hi);
-        const bool any_mask = __any_sync(0xffffffffu, need_mask);
+        // (warp-uniform without a vote per block: compared with the warp's extreme bounds)
+        const bool any_mask = !(mbase >= warp_lo && mbase + kWgCols - 1 <= warp_hi);
         // exponent arguments: scaled score (+ bias) minus the row's logsumexp, all in log2 units.
         // Common case: one packed FMA per two elements.  With bias, or when the logsumexp is so
         // large that product rounding matters (the aux warp flags that), scale first and subtract
@@ -877,6 +879,8 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       if (hi < row_hi) row_hi = (int)(hi < -1 ? -1 : hi);
     }
     if (m >= sq.sq) { row_lo = 1; row_hi = 0; }
+    // the tightest bounds over the warp's rows: a block needs masking iff it is not inside them
+    const int warp_lo = __reduce_max_sync(0xffffffffu, row_lo), warp_hi = __reduce_min_sync(0xffffffffu, row_hi);
     const int64_t lrow = lse_offset(p, sq, h);
     const float lse2 = (m < sq.sq) ? p.lse[lrow + m] * kLog2e : INFINITY;
     const float dlt = (m < sq.sq) ? p.delta[lrow + m] : 0.f;
@@ -907,8 +911,8 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[L::bSRead]);
       if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 6);
-      const bool need_mask = !(nbase >= row_lo && nbase + kWgCols - 1 <= row_hi);
-      const bool any_mask = __any_sync(0xffffffffu, need_mask);
+      // (warp-uniform without a vote per block: compared with the warp's extreme bounds)
+      const bool any_mask = !(nbase >= warp_lo && nbase + kWgCols - 1 <= warp_hi);
       if (simple) {
         const float2 sc2 = make_float2(p.qk_scale, p.qk_scale), nl2 = make_float2(-lse2, -lse2);
 #pragma unroll

@@ -306,6 +306,8 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       if (hi < row_hi) row_hi = (int)(hi < -1 ? -1 : hi);
     }
     if (m >= sq.sq) { row_lo = 1; row_hi = 0; }
+    // the tightest bounds over the warp's rows: a block needs masking iff it is not inside them
+    const int warp_lo = __reduce_max_sync(0xffffffffu, row_lo), warp_hi = __reduce_min_sync(0xffffffffu, row_hi);
     DropoutCtx dctx;
     if (p.dropout_on) dctx = dropout_ctx(p, z, h);
     const T* bias_row = nullptr;
@@ -330,8 +332,8 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       // magnitudes) keeps the raw scores and folds scale and maximum into one FMA per element
       // later.  Otherwise the scaled scores are formed first, so that equal raw scores give
       // exactly equal arguments however large they are.
-      const bool need_mask = !(n0 >= row_lo && n0 + kBN - 1 <= row_hi);
-      const bool any_mask = __any_sync(0xffffffffu, need_mask);
+      // (warp-uniform without a vote per block: compared with the warp's extreme bounds)
+      const bool any_mask = !(n0 >= warp_lo && n0 + kBN - 1 <= warp_hi);
       bool simple = !p.has_bias && p.qk_scale > 0.f;
       float mx;
       if (simple) {
