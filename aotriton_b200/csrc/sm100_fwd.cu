@@ -443,12 +443,11 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
           }
         }
         // P over the first 64 columns of this S buffer, two 16-bit values per column.
+        {
+          uint32_t pk[32];
 #pragma unroll
-        for (int c = half * 2; c < half * 2 + 2; ++c) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(sc[c * 32 + 2 * i], sc[c * 32 + 2 * i + 1]);
-          tmem_st16(s_addr + c * 16, pk);
+          for (int i = 0; i < 32; ++i) pk[i] = pack2<T>(sc[half * 64 + 2 * i], sc[half * 64 + 2 * i + 1]);
+          tmem_st32(s_addr + half * 32, pk);
         }
         if (half == 0) {
           tmem_wait_st();
