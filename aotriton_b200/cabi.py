@@ -22,7 +22,7 @@ SYMBOLS = [
     "ab200_attn_fwd", "ab200_attn_bwd", "ab200_attn_bwd_static_scratch", "ab200_bwd_preprocess", "ab200_bwd_dkdv", "ab200_bwd_dq",
     "ab200_debug_simulate_encoded_softmax", "ab200_check_gpu", "ab200_multiprocessor_count",
     "ab200_set_kernel_family", "ab200_last_fwd_family", "ab200_last_bwd_family", "ab200_kernel_status",
-    "ab200_launch_count",
+    "ab200_stream_check", "ab200_debug_bounded_wait_test", "ab200_launch_count",
     "ab200_version",
 ]
 
@@ -84,6 +84,9 @@ def lib() -> C.CDLL:
         L.ab200_set_kernel_family.argtypes = [C.c_int]
         L.ab200_kernel_status.argtypes = [C.c_int]
         L.ab200_kernel_status.restype = C.c_uint
+        L.ab200_stream_check.argtypes = [C.c_void_p]
+        L.ab200_debug_bounded_wait_test.argtypes = [C.c_int, C.c_uint]
+        L.ab200_debug_bounded_wait_test.restype = None
         L.ab200_launch_count.restype = C.c_uint64
         L.ab200_version.restype = C.c_char_p
         _lib = L

@@ -20,12 +20,19 @@ namespace ab200 {
 static std::atomic<uint64_t> g_launches{0};
 static thread_local int g_family = 0;   // per calling thread, so concurrent callers do not interfere
 static thread_local int t_last_fwd = 0, t_last_bwd = 0;
+// Test hook of the bounded waits (ab200_debug_bounded_wait_test): which copy the producer leaves
+// out and the wait limit of the calling thread's next launches.
+static thread_local int t_drop_copy = 0;
+static thread_local unsigned int t_wait_limit_kcycles = 0;
+// Devices on which a kernel reported that a bounded wait ran out (seen by ab200_kernel_status or
+// ab200_stream_check): further launches there are refused until the word is reset.
+static std::atomic<uint64_t> g_failed_devices{0};
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 namespace {
 
-enum : int { kErrInvalidValue = 1, kErrNoBinaryForGpu = 209, kErrNotSupported = 801 };
+enum : int { kErrInvalidValue = 1, kErrNoBinaryForGpu = 209, kErrLaunchFailure = 719, kErrNotSupported = 801 };
 
 struct DeviceInfo { int major = 0, minor = 0, sms = 0; bool known = false; };
 
@@ -65,7 +72,28 @@ int check_device(cudaStream_t st) {
   if (dev < 0) return kErrNoBinaryForGpu;
   DeviceInfo d = device_info(dev);
   if (!d.known || d.major != 10) return kErrNoBinaryForGpu;   // kernels are built for sm_100a only
+  if (dev < 64 && ((g_failed_devices.load(std::memory_order_relaxed) >> dev) & 1u)) return kErrLaunchFailure;
   return 0;
+}
+
+// The stream decides the device (like the reference, which derives everything from the stream):
+// while an entry point runs, the stream's device is the current one, so that launches, symbol
+// look-ups and attribute settings all address it even if the caller's current device differs.
+struct DeviceGuard {
+  int old_ = -1;
+  bool switched_ = false;
+  explicit DeviceGuard(cudaStream_t st) {
+    const int dev = stream_device(st);
+    if (dev >= 0 && cudaGetDevice(&old_) == cudaSuccess && old_ != dev)
+      switched_ = cudaSetDevice(dev) == cudaSuccess;
+    (void)cudaGetLastError();
+  }
+  ~DeviceGuard() { if (switched_) { (void)cudaSetDevice(old_); } }
+};
+
+bool rows_16byte(const ab200_view4& v) {
+  return v.ptr != nullptr && (reinterpret_cast<uintptr_t>(v.ptr) & 15u) == 0 && v.stride[3] == 1 &&
+         v.stride[0] % 8 == 0 && v.stride[1] % 8 == 0 && v.stride[2] % 8 == 0;
 }
 
 View4 to_view(const ab200_view4& v) {
@@ -105,6 +133,7 @@ int fill_common(const ab200_attn_problem& a, Params& p) {
   }
   p.seed_ptr = a.philox_seed; p.off1_ptr = a.philox_offset1; p.off2 = a.philox_offset2;
   p.philox_head_offset = a.philox_head_offset; p.philox_hq = a.philox_num_head_q;
+  p.wait_limit_kcycles = t_wait_limit_kcycles; p.drop_copy = t_drop_copy;
   return 0;
 }
 
@@ -134,7 +163,26 @@ int ab200_last_fwd_family(void) { return t_last_fwd; }
 int ab200_last_bwd_family(void) { return t_last_bwd; }
 unsigned int ab200_kernel_status(int reset) {
   unsigned int f = sm100_fwd_status(reset != 0), b = sm100_bwd_status(reset != 0);
-  return f ? f : b;
+  const unsigned int v = f ? f : b;
+  int dev = -1;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+    if (reset) g_failed_devices.fetch_and(~(uint64_t(1) << dev));
+    else if (v != 0 && v != 0xffffffffu) g_failed_devices.fetch_or(uint64_t(1) << dev);
+  }
+  return v;
+}
+
+int ab200_stream_check(void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DeviceGuard guard(st);
+  cudaError_t e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return (int)e;
+  return ab200_kernel_status(0) != 0 ? kErrLaunchFailure : 0;
+}
+
+void ab200_debug_bounded_wait_test(int drop_copy, unsigned int wait_limit_kcycles) {
+  t_drop_copy = (drop_copy >= 0 && drop_copy <= 3) ? drop_copy : 0;
+  t_wait_limit_kcycles = wait_limit_kcycles;
 }
 uint64_t ab200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 const char* ab200_version(void) { return "aotriton_b200 0.1 (sm_100a; API level of aotriton 0.14)"; }
@@ -146,6 +194,7 @@ int ab200_debug_simulate_encoded_softmax(const ab200_view4* r, int32_t dtype, in
   if (dtype < AB200_DTYPE_FP32 || dtype > AB200_DTYPE_BF16) return kErrNotSupported;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (int e = check_device(st)) return e;
+  DeviceGuard guard(st);
   return (int)launch_dropout_sign(dtype, to_view(*r), batch, num_head_q, rows, cols, dropout_p, philox_seed,
                                   philox_offset1, philox_offset2, st);
 }
@@ -159,8 +208,9 @@ int ab200_attn_fwd(const ab200_attn_fwd_args* a, void* stream) {
   if (!inner_contiguous(a->q) || !inner_contiguous(a->k) || !inner_contiguous(a->v) || !inner_contiguous(a->out))
     return kErrInvalidValue;
   if (int e = check_device(st)) return e;
+  DeviceGuard guard(st);
   p.q = to_view(a->q); p.k = to_view(a->k); p.v = to_view(a->v); p.out = to_view(a->out);
-  p.bias = to_view(a->bias); p.has_bias = a->bias.ptr != nullptr;
+  p.bias = to_view(a->bias); p.has_bias = a->bias.ptr != nullptr; p.bias_vec = rows_16byte(a->bias);
   p.lse = a->lse;
   p.seed_out = a->philox_seed_output; p.off_out = a->philox_offset_output;
 
@@ -199,7 +249,7 @@ static int fill_bwd(const ab200_attn_bwd_args* a, Params& p, bool need_outputs) 
       return kErrInvalidValue;
   }
   p.q = to_view(a->q); p.k = to_view(a->k); p.v = to_view(a->v);
-  p.bias = to_view(a->bias); p.has_bias = a->bias.ptr != nullptr;
+  p.bias = to_view(a->bias); p.has_bias = a->bias.ptr != nullptr; p.bias_vec = rows_16byte(a->bias);
   p.dq = to_view(a->dq); p.dk = to_view(a->dk); p.dv = to_view(a->dv); p.dbias = to_view(a->dbias);
   // dBias is skipped when absent or when all its strides are zero
   // (modules/flash/kernel/bwd_kernel_dq.py:265-266).
@@ -213,6 +263,7 @@ int ab200_bwd_preprocess(const ab200_attn_bwd_args* a, void* stream) {
   Params p{};
   if (int e = fill_bwd(a, p, false)) return e;
   if (int e = check_device(st)) return e;
+  DeviceGuard guard(st);
   return (int)launch_preprocess(a->prob.dtype, p, st);
 }
 
@@ -222,6 +273,7 @@ int ab200_bwd_dkdv(const ab200_attn_bwd_args* a, void* stream) {
   if (int e = fill_bwd(a, p, true)) return e;
   if (!a->dk.ptr || !a->dv.ptr) return kErrInvalidValue;
   if (int e = check_device(st)) return e;
+  DeviceGuard guard(st);
   const int family = g_family;
   if (want_sm100(family) && sm100_bwd_supported(a->prob.dtype, p)) {
     t_last_bwd = 2;
@@ -238,6 +290,7 @@ int ab200_bwd_dq(const ab200_attn_bwd_args* a, void* stream) {
   if (int e = fill_bwd(a, p, true)) return e;
   if (!a->dq.ptr) return kErrInvalidValue;
   if (int e = check_device(st)) return e;
+  DeviceGuard guard(st);
   const int family = g_family;
   if (want_sm100(family) && sm100_bwd_supported(a->prob.dtype, p)) {
     t_last_bwd = 2;
@@ -289,8 +342,18 @@ int ab200_attn_bwd_static_scratch(const ab200_attn_bwd_args* a, void* stream) {
   // Rows of the logsumexp / delta matrix: dense and padded layouts are (batch*Hq, max_sq);
   // token-packed varlen is (Hq, tokens in the packed q tensor).
   const bool packed = pr.cu_seqlens_q != nullptr && pr.varlen_type != AB200_VARLEN_PADDED;
-  const long long need = packed ? (long long)pr.num_head_q * (long long)a->q.size[2]
-                                : (long long)pr.batch * (long long)pr.num_head_q * (long long)pr.max_seqlen_q;
+  // The kernels index delta up to the packed token count, which they read on the device
+  // (cu_seqlens_q[batch], or seq_strides_q[batch]); the host can only bound it by the extent the
+  // caller declares for q, so a packed call without that extent is refused.
+  if (packed && a->q.size[2] <= 0) {
+    std::fprintf(stderr, "[aotriton_b200] ab200_attn_bwd_static_scratch: token-packed varlen needs q.size[2] "
+                         "(the packed token count) to bound the built-in scratch\n");
+    return kErrInvalidValue;
+  }
+  const long long dense_rows = (long long)pr.batch * (long long)pr.max_seqlen_q;
+  const long long tokens = packed ? ((long long)a->q.size[2] < dense_rows ? (long long)a->q.size[2] : dense_rows)
+                                  : dense_rows;
+  const long long need = (long long)pr.num_head_q * tokens;
   if (need < 0 || need > (long long)AB200_STATIC_DELTA_FLOATS) {
     std::fprintf(stderr,
                  "[aotriton_b200] ab200_attn_bwd_static_scratch: delta needs %lld floats, the built-in scratch "
@@ -300,6 +363,7 @@ int ab200_attn_bwd_static_scratch(const ab200_attn_bwd_args* a, void* stream) {
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (int e = check_device(st)) return e;
+  DeviceGuard guard(st);
   cudaError_t cerr;
   float* delta = static_delta_address(stream_device(st), &cerr);
   if (delta == nullptr) return (int)cerr;

@@ -47,6 +47,10 @@ struct Params {
   uint64_t *seed_out, *off_out;
   int32_t philox_head_offset, philox_hq;
   int32_t has_bias, has_dbias;
+  int32_t bias_vec;               // bias rows are 16-byte aligned and unit-stride: read eight values per load
+  uint32_t wait_limit_kcycles;    // bound of every in-kernel wait, in units of 1024 SM cycles (0 = about a second)
+  int32_t drop_copy;              // test hook of the bounded waits: the producer leaves out one tile copy
+                                  // (1 = first V block of the forward, 2 = first Q/dO block of dK/dV, 3 = first V block of dQ)
 };
 
 // Geometry of one (sequence z) slice.

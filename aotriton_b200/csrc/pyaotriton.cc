@@ -6,8 +6,11 @@
 // Differences a caller can observe:
 //   * Stream(handle: int) is accepted in addition to Stream(); handle is a
 //     cudaStream_t as an integer (torch.cuda.current_stream().cuda_stream).
-//   * lazy_tensor.* allocate through a small caching pool over cudaMalloc instead of
-//     libtorch, so the module does not link against torch.
+//   * lazy_tensor.dq_acc / delta allocate through a small stream-keyed caching pool over
+//     cudaMalloc, so the module does not link against libtorch; lazy_tensor.dq_acc_from /
+//     delta_from take a Python callable instead, which is how the torch allocator is used
+//     (the reference's lazy tensors call at::zeros / at::empty,
+//     bindings/lazy_tensor/lazy_tensor_template.h:19-97).
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
@@ -18,6 +21,7 @@
 
 #include <map>
 #include <mutex>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -27,18 +31,19 @@ namespace aotriton = AOTRITON_NS;
 namespace {
 
 // ---- device scratch pool for lazy tensors -------------------------------------
-// Blocks go back to a per-device free list instead of cudaFree, so disposing a lazy
-// tensor right after an asynchronous launch never synchronises the device.  A block
-// is reused only by later calls, which queue behind the earlier kernels when they use
-// the same stream (the same assumption a stream-ordered caching allocator makes).
+// Blocks go back to a free list instead of cudaFree, so disposing a lazy tensor right after an
+// asynchronous launch never synchronises the device.  The free lists are keyed by (device,
+// stream): a block is only handed out again for work on the stream its previous user ran on,
+// where the new kernels queue behind the old ones (what a stream-ordered caching allocator does).
 class ScratchPool {
  public:
-  void* take(int device, size_t bytes) {
+  using Key = std::pair<int, intptr_t>;
+  void* take(int device, intptr_t stream, size_t bytes) {
     bytes = (bytes + 511) & ~size_t(511);
     if (bytes == 0) bytes = 512;
     {
       std::lock_guard<std::mutex> lock(mu_);
-      auto& fl = free_[device];
+      auto& fl = free_[Key(device, stream)];
       auto it = fl.lower_bound(bytes);
       if (it != fl.end() && it->first <= 2 * bytes) {
         void* p = it->second;
@@ -58,15 +63,15 @@ class ScratchPool {
     sizes_[p] = bytes;
     return p;
   }
-  void give(int device, void* p) {
+  void give(int device, intptr_t stream, void* p) {
     if (!p) return;
     std::lock_guard<std::mutex> lock(mu_);
-    free_[device].emplace(sizes_[p], p);
+    free_[Key(device, stream)].emplace(sizes_[p], p);
   }
 
  private:
   std::mutex mu_;
-  std::map<int, std::multimap<size_t, void*>> free_;
+  std::map<Key, std::multimap<size_t, void*>> free_;
   std::map<void*, size_t> sizes_;
 };
 
@@ -75,36 +80,67 @@ ScratchPool& pool() {
   return *p;
 }
 
+// Cookies of lazy tensors that have not been disposed yet.  A LazyTensor is a plain struct that
+// callers copy around (into the params struct, for one); only the copy inside the operator call
+// is cleared by free(), so a stale copy used for a second call must be recognised here.
+class LiveCookies {
+ public:
+  void add(void* c) { std::lock_guard<std::mutex> l(mu_); live_.insert(c); }
+  bool alive(void* c) { std::lock_guard<std::mutex> l(mu_); return live_.count(c) != 0; }
+  bool remove(void* c) { std::lock_guard<std::mutex> l(mu_); return live_.erase(c) != 0; }
+ private:
+  std::mutex mu_;
+  std::set<void*> live_;
+};
+LiveCookies& cookies() {
+  static LiveCookies* c = new LiveCookies;
+  return *c;
+}
+
+template <int Rank>
+aotriton::TensorView<Rank> contiguous_f32_view(const aotriton::TensorView<Rank>& like, void* mem, uint64_t* numel) {
+  std::array<uint64_t, Rank> sizes = like.sizes(), strides{};
+  uint64_t n = 1;
+  for (int i = Rank - 1; i >= 0; --i) { strides[i] = n; n *= sizes[i]; }
+  if (numel) *numel = n;
+  return aotriton::TensorView<Rank>(reinterpret_cast<intptr_t>(mem), sizes, strides, aotriton::kFloat32);
+}
+
 template <int Rank, bool Zeroed>
 struct LazyHelper {
   struct Ctx {
     aotriton::TensorView<Rank> like;
     int device;
+    intptr_t stream;      // the stream the operator call will launch on (0 = the default stream)
     void* mem = nullptr;
   };
   static aotriton::TensorView<Rank> acquire(aotriton::LazyTensor<Rank>* self) {
     auto* ctx = static_cast<Ctx*>(self->cookie);
-    if (!ctx) return aotriton::TensorView<Rank>();   // already disposed: a lazy tensor serves one call
-    std::array<uint64_t, Rank> sizes = ctx->like.sizes(), strides{};
-    uint64_t n = 1;
-    for (int i = Rank - 1; i >= 0; --i) { strides[i] = n; n *= sizes[i]; }
+    if (!ctx || !cookies().alive(ctx)) return aotriton::TensorView<Rank>();   // a lazy tensor serves one call
+    uint64_t n = 0;
+    contiguous_f32_view<Rank>(ctx->like, nullptr, &n);
     if (!ctx->mem) {
-      ctx->mem = pool().take(ctx->device, n * sizeof(float));
-      if (ctx->mem && Zeroed) cudaMemsetAsync(ctx->mem, 0, n * sizeof(float), nullptr);
+      ctx->mem = pool().take(ctx->device, ctx->stream, n * sizeof(float));
+      if (ctx->mem && Zeroed)
+        cudaMemsetAsync(ctx->mem, 0, n * sizeof(float), reinterpret_cast<cudaStream_t>(ctx->stream));
     }
-    return aotriton::TensorView<Rank>(reinterpret_cast<intptr_t>(ctx->mem), sizes, strides, aotriton::kFloat32);
+    if (!ctx->mem) return aotriton::TensorView<Rank>();
+    return contiguous_f32_view<Rank>(ctx->like, ctx->mem, nullptr);
   }
   static void dispose(aotriton::LazyTensor<Rank>* self) {
     auto* ctx = static_cast<Ctx*>(self->cookie);
-    pool().give(ctx->device, ctx->mem);
+    if (!ctx || !cookies().remove(ctx)) return;
+    pool().give(ctx->device, ctx->stream, ctx->mem);
     delete ctx;
   }
   static aotriton::TensorView<Rank> acquire_eager(aotriton::LazyTensor<Rank>* self) { return self->eager; }
 
-  static aotriton::LazyTensor<Rank> make(const aotriton::TensorView<Rank>& like, int device) {
+  static aotriton::LazyTensor<Rank> make(const aotriton::TensorView<Rank>& like, int device, intptr_t stream) {
     auto* ctx = new Ctx;
     ctx->like = like;
     ctx->device = device;
+    ctx->stream = stream;
+    cookies().add(ctx);
     aotriton::LazyTensor<Rank> lt;
     lt.cookie = ctx;
     lt.acquire = &acquire;
@@ -115,6 +151,48 @@ struct LazyHelper {
     aotriton::LazyTensor<Rank> lt;
     lt.acquire = &acquire_eager;
     lt.eager = view;
+    return lt;
+  }
+};
+
+// Lazy tensor whose memory comes from a Python callable (called at most once, when the operator
+// really needs the tensor): the callable returns an object with data_ptr(), e.g. a torch tensor
+// made by torch.empty / torch.zeros on the current stream, which the lazy tensor keeps alive until
+// the operator disposes of it.  The operator runs with the GIL released, so both callbacks take it.
+template <int Rank>
+struct PyLazy {
+  struct Ctx {
+    aotriton::TensorView<Rank> like;
+    py::object factory, tensor;
+  };
+  static aotriton::TensorView<Rank> acquire(aotriton::LazyTensor<Rank>* self) {
+    auto* ctx = static_cast<Ctx*>(self->cookie);
+    if (!ctx || !cookies().alive(ctx)) return aotriton::TensorView<Rank>();
+    py::gil_scoped_acquire gil;
+    try {
+      if (!ctx->tensor || ctx->tensor.is_none()) ctx->tensor = ctx->factory();
+      const intptr_t ptr = ctx->tensor.attr("data_ptr")().template cast<intptr_t>();
+      return contiguous_f32_view<Rank>(ctx->like, reinterpret_cast<void*>(ptr), nullptr);
+    } catch (py::error_already_set& e) {
+      e.discard_as_unraisable("pyaotriton lazy tensor factory");
+      return aotriton::TensorView<Rank>();
+    }
+  }
+  static void dispose(aotriton::LazyTensor<Rank>* self) {
+    auto* ctx = static_cast<Ctx*>(self->cookie);
+    if (!ctx || !cookies().remove(ctx)) return;
+    py::gil_scoped_acquire gil;
+    delete ctx;
+  }
+  static aotriton::LazyTensor<Rank> make(const aotriton::TensorView<Rank>& like, py::object factory) {
+    auto* ctx = new Ctx;
+    ctx->like = like;
+    ctx->factory = std::move(factory);
+    cookies().add(ctx);
+    aotriton::LazyTensor<Rank> lt;
+    lt.cookie = ctx;
+    lt.acquire = &acquire;
+    lt.dispose = &dispose;
     return lt;
   }
 };
@@ -253,8 +331,10 @@ void def_lazy(py::module_& root) {
   py::module_ m = root.def_submodule("lazy_tensor", "lazy_tensor API namespace");
   py::class_<aotriton::LazyTensor<4>>(m, "LT4");
   py::class_<aotriton::LazyTensor<2>>(m, "LT2");
-  m.def("dq_acc", &LazyHelper<4, true>::make);
-  m.def("delta", &LazyHelper<2, false>::make);
+  m.def("dq_acc", &LazyHelper<4, true>::make, py::arg("like"), py::arg("device"), py::arg("stream") = 0);
+  m.def("delta", &LazyHelper<2, false>::make, py::arg("like"), py::arg("device"), py::arg("stream") = 0);
+  m.def("dq_acc_from", &PyLazy<4>::make, py::arg("like"), py::arg("factory"));
+  m.def("delta_from", &PyLazy<2>::make, py::arg("like"), py::arg("factory"));
   m.def("eager_delta", &LazyHelper<2, false>::make_eager);
   m.def("eager_null_dq_acc", &LazyHelper<4, false>::make_eager);
 }
@@ -309,6 +389,9 @@ PYBIND11_MODULE(pyaotriton, m) {
   m.def("set_kernel_family", [](int f) { return ab200_set_kernel_family(f); });
   m.def("last_fwd_family", []() { return ab200_last_fwd_family(); });
   m.def("last_bwd_family", []() { return ab200_last_bwd_family(); });
+  m.def("stream_check", [](aotriton::Stream s) { return static_cast<hipError_t>(ab200_stream_check(s.native())); },
+        py::call_guard<py::gil_scoped_release>(), py::arg("stream") = aotriton::Stream());
+  m.def("kernel_status", [](bool reset) { return ab200_kernel_status(reset ? 1 : 0); }, py::arg("reset") = false);
   def_v2(m);
   def_v3(m);
   def_lazy(m);

@@ -104,8 +104,8 @@ struct BwdSmem {
                        bResEmpty = 15, bPFull = 16, bSchedFull = 17, bSchedEmpty = 19,
                        bCount = 21;
   static constexpr int kTmemSlot = kBars + bCount * 8;
-  static constexpr int kAbort = kTmemSlot + 4;
-  static constexpr int kUsed = kAbort + 4;
+  static constexpr int kAbort = kTmemSlot + 4;           // abort word, then the launch's wait limit
+  static constexpr int kUsed = kAbort + 8;
   // The tiles need 1024-byte alignment, which is established at run time; the kernel checks that
   // the padding it needed still fits (without static shared memory the base is aligned already).
   static constexpr int kDynamic = kUsed + 512;
@@ -151,9 +151,9 @@ __device__ void zero_rows(const View4& v, int b, int h, int64_t tok0, int row0, 
 }
 
 template <int HD>
-__device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t* abort_flag) {
+__device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t* abort_flag, uint32_t limit_kcycles) {
   using L = BwdSmem<HD>;
-  *abort_flag = 0;
+  init_abort_and_limit(abort_flag, limit_kcycles);
   mbar_init(&bars[L::bResFull], 1);
   for (int s = 0; s < 2; ++s) {
     mbar_init(&bars[L::bRingFull + s], 1);
@@ -229,7 +229,8 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
   volatile int* sched = reinterpret_cast<volatile int*>(smem + L::kSched);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
+  // An earlier CTA timed out: the whole CTA leaves (one read, one CTA-wide decision).
+  if (__syncthreads_or(threadIdx.x == 0 && *reinterpret_cast<volatile unsigned int*>(status) != 0u)) return;
   if ((int)(smem - smem_raw) + L::kUsed > L::kDynamic) {      // the alignment padding did not fit
     if (threadIdx.x == 0) atomicCAS(status, 0u, 0x1F00u);
     return;
@@ -252,7 +253,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
   };
 
   if (threadIdx.x == 0) {
-    init_barriers<HD>(bars, abort_flag);
+    init_barriers<HD>(bars, abort_flag, p.wait_limit_kcycles);
     prefetch_tmap(&tm_q); prefetch_tmap(&tm_k); prefetch_tmap(&tm_v); prefetch_tmap(&tm_do);
   }
   if (warp == 1) {
@@ -286,6 +287,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           const int mrow = (int)(it.sq.q0 + (int64_t)(it.mb_lo + mb) * kBlk);
           if (++mb == it.nmb) { mb = 0; ++hg; }
           if (!mbar_wait(&bars[L::bRingEmpty + s], ((G >> 1) & 1u) ^ 1u, abort_flag, status, 0x1100)) { ok = false; break; }
+          if (p.drop_copy == 2 && G == 0) continue;   // test hook: this Q/dO block never arrives
           mbar_expect_tx(&bars[L::bRingFull + s], 2 * L::kTile);
           for (int hf = 0; hf < L::kHalves; ++hf) {
             tma_load_4d(smem + L::kRingA + s * L::kTile + hf * 16384, &tm_q, &bars[L::bRingFull + s], hf * 64, mrow, h,
@@ -298,8 +300,11 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       }
       if (*abort_flag) {
         // Let copies that are still in flight land before the CTA gives its shared memory back.
-        if (live > 0) mbar_wait_quiet(&bars[L::bResFull], (live - 1) & 1u);
-        for (uint32_t g = (G >= 2 ? G - 2 : 0); g < G; ++g) mbar_wait_quiet(&bars[L::bRingFull + (g & 1u)], (g >> 1) & 1u);
+        if (live > 0) mbar_wait_quiet(&bars[L::bResFull], (live - 1) & 1u, abort_flag);
+        for (uint32_t g = (G >= 2 ? G - 2 : 0); g < G; ++g) {
+          if (p.drop_copy == 2 && g == 0) continue;   // (never issued)
+          mbar_wait_quiet(&bars[L::bRingFull + (g & 1u)], (g >> 1) & 1u, abort_flag);
+        }
       }
     }
     __syncwarp();
@@ -307,8 +312,12 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     // ================================= MMA issuer ====================================
     // The whole warp walks the loop and waits; one elected lane issues.  With warp-uniform control
     // flow the descriptors stay in uniform registers and a GEMM costs few issue slots.
+    // Contractions over a head dimension run over it rounded up to 16, products into a head
+    // dimension produce it rounded up to 16 (the copies zero-fill up to the 64-column box).
     constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
-    constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
+    const uint32_t kIdescDV = instr_desc_f16(Fmt<T>::code, 128, (uint32_t)((p.dvo + 15) & ~15), 0, 1);
+    const uint32_t kIdescDK = instr_desc_f16(Fmt<T>::code, 128, (uint32_t)((p.dqk + 15) & ~15), 0, 1);
+    const int ksteps_qk = (p.dqk + 15) >> 4, ksteps_vo = (p.dvo + 15) >> 4;
     constexpr uint32_t kStageStep = L::kTile >> 4;
     const uint64_t k_km = kmajor_base(smem_u32(smem + L::kResA)), v_km = kmajor_base(smem_u32(smem + L::kResB));
     const uint64_t q_km = kmajor_base(smem_u32(smem + L::kRingA)), do_km = kmajor_base(smem_u32(smem + L::kRingB));
@@ -321,7 +330,8 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tmem_base + kColS, k_km + kmajor_step(kk), qa + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
+          if (kk < ksteps_qk)
+            mma_ss(tmem_base + kColS, k_km + kmajor_step(kk), qa + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
         mma_commit(&bars[L::bSFull + (g & 1u)]);
       }
       __syncwarp();
@@ -332,7 +342,8 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tmem_base + kColDP, v_km + kmajor_step(kk), da + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
+          if (kk < ksteps_vo)
+            mma_ss(tmem_base + kColDP, v_km + kmajor_step(kk), da + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
         mma_commit(&bars[L::bDpFull]);
         if (release_kv) mma_commit(&bars[L::bResEmpty]);
       }
@@ -349,16 +360,28 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       if (G > 0 && !wait(L::bSRead, (G - 1) & 1u, 0x1201)) break;
       if (!wait(L::bRingFull + (G & 1u), (G >> 1) & 1u, 0x1202)) break;
       if (lane == 0) AB200_STAMP(G, 15);
+      // Last, partial query block of the sequence: rows of Q and dO beyond its end must not reach
+      // the dV / dK products (a zero probability times a non-finite value would poison them).
+      auto zero_ring_tail = [&](uint32_t g, int mb) {
+        const int valid = it.sq.sq - (it.mb_lo + mb) * kBlk;
+        if (valid < kBlk) {
+          zero_tail_rows(smem + L::kRingA + (g & 1u) * L::kTile, valid, L::kHalves, lane);
+          zero_tail_rows(smem + L::kRingB + (g & 1u) * L::kTile, valid, L::kHalves, lane);
+        }
+      };
+      zero_ring_tail(G, 0);
       tc_fence_after();
       issue_s(G);
       issue_dp(G, it.niter == 1);
       if (lane == 0) AB200_STAMP(G, 8);
-      for (int i = 0; i < it.niter; ++i, ++G) {
+      for (int i = 0, mb_next = 1; i < it.niter; ++i, ++G, ++mb_next) {     // mb_next: (i + 1) % nmb
         const uint32_t s = G & 1u, par = G & 1u;
+        if (mb_next == it.nmb) mb_next = 0;
         if (i + 1 < it.niter) {
           // S_g sits in registers of every compute thread: its buffer can take S_{g+1} already.
           if (!wait(L::bSRead, par, 0x1300)) { ok = false; break; }
           if (!wait(L::bRingFull + ((G + 1) & 1u), ((G + 1) >> 1) & 1u, 0x1400)) { ok = false; break; }
+          zero_ring_tail(G + 1, mb_next);
           tc_fence_after();
           issue_s(G + 1);
         }
@@ -370,7 +393,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           const uint64_t da = do_mn + (uint64_t)(s * kStageStep);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tmem_base + kColAcc0, tmem_base + kColDP + split_a_col(kk), da + mnmajor_step(kk), kIdescTS,
+            mma_ts(tmem_base + kColAcc0, tmem_base + kColDP + split_a_col(kk), da + mnmajor_step(kk), kIdescDV,
                    kk > 0 ? 1u : first);
         }
         __syncwarp();
@@ -381,7 +404,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           const uint64_t qa = q_mn + (uint64_t)(s * kStageStep);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + 16u + split_a_col(kk), qa + mnmajor_step(kk), kIdescTS,
+            mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + 16u + split_a_col(kk), qa + mnmajor_step(kk), kIdescDK,
                    kk > 0 ? 1u : first);
           mma_commit(&bars[L::bRingEmpty + s]);
           if (i + 1 == it.niter) mma_commit(&bars[L::bAccDone]);
@@ -550,12 +573,21 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 7);
         uint32_t keep = 0xffffffffu;
         if (p.dropout_on) {
+          // One Philox counter serves four consecutive keys of one query row, and the four lanes of
+          // a quad own exactly such keys (same n >> 2): lane q4 of the quad draws the counters of
+          // query rows mbase + q4 + 4k (k = 0..7) for all four keys, then the quad exchanges them.
           const DropoutCtx dctx = dropout_ctx(p, z, h);
-          const int nn = min(n, p.max_sk - 1);
+          const int q4 = lane & 3;
+          uint32_t mine = 0u;            // nibble k: keep bits of keys 4a..4a+3 for query row mbase + q4 + 4k
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            mine |= dropout_keep4(dctx, min(mbase + q4 + 4 * k, p.max_sq - 1), n >> 2) << (4 * k);
           keep = 0u;
 #pragma unroll
-          for (int c = 0; c < 32; ++c)
-            if (dropout_keep(dctx, min(mbase + c, p.max_sq - 1), nn)) keep |= (1u << c);
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t w = __shfl_sync(0xffffffffu, mine, (lane & ~3) | i);
+            keep |= ((w >> q4) & 0x11111111u) << i;      // this lane's key, query rows mbase + i + 4k -> bit 4k + i
+          }
         }
         if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 1);
         if (!mbar_wait(&bars[L::bDpFull], par, abort_flag, status, 0x1900)) { ok = false; break; }
@@ -668,7 +700,7 @@ struct DqSmem {
                        bDpFull = 13, bDsFull = 15, bAccDone = 17, bCount = 18;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
-  static constexpr int kDynamic = kAbort + 4 + 1024;
+  static constexpr int kDynamic = kAbort + 8 + 1024;
 };
 
 // =========================================================================================
@@ -688,7 +720,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int z = blockIdx.z, h = blockIdx.y;
   const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * kBlk;
-  if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
+  if (__syncthreads_or(threadIdx.x == 0 && *reinterpret_cast<volatile unsigned int*>(status) != 0u)) return;
   const Seq sq = resolve_seq(p, z);
   if (m0 >= sq.sq) return;
   const int hk = h / p.group;
@@ -702,7 +734,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
   const int niter = n_hi / kBlk - jb_lo + 1;
 
   if (threadIdx.x == 0) {
-    *abort_flag = 0;
+    init_abort_and_limit(abort_flag, p.wait_limit_kcycles);
     mbar_init(&bars[L::bResFull], 1);
     for (int s = 0; s < L::kKStages; ++s) { mbar_init(&bars[L::bKFull + s], 1); mbar_init(&bars[L::bKEmpty + s], 1); }
     for (int s = 0; s < 2; ++s) {
@@ -729,6 +761,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       mbar_expect_tx(&bars[L::bKFull + i], L::kTile);
       for (int hf = 0; hf < L::kHalves; ++hf)
         tma_load_4d(smem + L::kK + i * L::kTile + hf * 16384, &tm_k, &bars[L::bKFull + i], hf * 64, krow, hk, sq.bidx);
+      if (p.drop_copy == 3 && i == 0) continue;   // test hook: this block's V never arrives
       mbar_expect_tx(&bars[L::bVFull + i], L::kTile);
       for (int hf = 0; hf < L::kHalves; ++hf)
         tma_load_4d(smem + L::kV + i * L::kTile + hf * 16384, &tm_v, &bars[L::bVFull + i], hf * 64, krow, hk, sq.bidx);
@@ -762,10 +795,13 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
         issued_v = i + 1;
       }
       if (*abort_flag) {
-        mbar_wait_quiet(&bars[L::bResFull], 0);
+        mbar_wait_quiet(&bars[L::bResFull], 0, abort_flag);
         for (int i = max(0, issued_k - L::kKStages); i < issued_k; ++i)
-          mbar_wait_quiet(&bars[L::bKFull + i % L::kKStages], (uint32_t)(i / L::kKStages) & 1u);
-        for (int i = max(0, issued_v - 2); i < issued_v; ++i) mbar_wait_quiet(&bars[L::bVFull + (i & 1)], (uint32_t)(i >> 1) & 1u);
+          mbar_wait_quiet(&bars[L::bKFull + i % L::kKStages], (uint32_t)(i / L::kKStages) & 1u, abort_flag);
+        for (int i = max(0, issued_v - 2); i < issued_v; ++i) {
+          if (p.drop_copy == 3 && i == 0) continue;   // (never issued)
+          mbar_wait_quiet(&bars[L::bVFull + (i & 1)], (uint32_t)(i >> 1) & 1u, abort_flag);
+        }
       }
     }
     __syncwarp();
@@ -774,7 +810,8 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     // flow warp-uniform lets the descriptors live in uniform registers, which makes the issue of
     // a GEMM several times cheaper in issue slots than a single-lane branch.
     constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
-    constexpr uint32_t kIdescTS = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
+    const uint32_t kIdescDQ = instr_desc_f16(Fmt<T>::code, 128, (uint32_t)((p.dqk + 15) & ~15), 0, 1);
+    const int ksteps_qk = (p.dqk + 15) >> 4, ksteps_vo = (p.dvo + 15) >> 4;
     constexpr uint32_t kStageStep = L::kTile >> 4;
     const uint64_t q_km = kmajor_base(smem_u32(smem + L::kResA)), do_km = kmajor_base(smem_u32(smem + L::kResB));
     const uint64_t k_km = kmajor_base(smem_u32(smem + L::kK)), v_km = kmajor_base(smem_u32(smem + L::kV));
@@ -782,23 +819,35 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     auto wait = [&](int bar, uint32_t parity, uint32_t where) {
       return __all_sync(0xffffffffu, mbar_wait(&bars[bar], parity, abort_flag, status, where)) != 0;
     };
+    // Last, partial key block of the sequence: rows of K and V beyond its end must not reach the
+    // dP and dQ products (a zero dS times a non-finite K row, or dO times a non-finite V row).
+    auto zero_tail = [&](int base, int i, int stage) {
+      const int valid = sq.sk - (jb_lo + i) * kBlk;
+      if (valid < kBlk) zero_tail_rows(smem + base + stage * L::kTile, valid, L::kHalves, lane);
+    };
     auto issue_s = [&](int i) {      // S = Q K_i^T
+      zero_tail(L::kK, i, i % L::kKStages);
+      tc_fence_after();
       const uint64_t ka = k_km + (uint64_t)((uint32_t)(i % L::kKStages) * kStageStep);
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(tmem_base + kColS, q_km + kmajor_step(kk), ka + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
+          if (kk < ksteps_qk)
+            mma_ss(tmem_base + kColS, q_km + kmajor_step(kk), ka + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
         mma_commit(&bars[L::bSFull]);
       }
       __syncwarp();
     };
     auto issue_dp = [&](int i) {     // dP = dO V_i^T, into dP buffer i & 1; frees V's ring stage
+      zero_tail(L::kV, i, i & 1);
+      tc_fence_after();
       const uint64_t va = v_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
       const uint32_t d = tmem_base + kColDP + (uint32_t)(i & 1) * 128u;
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          mma_ss(d, do_km + kmajor_step(kk), va + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
+          if (kk < ksteps_vo)
+            mma_ss(d, do_km + kmajor_step(kk), va + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
         mma_commit(&bars[L::bDpFull + (i & 1)]);
         mma_commit(&bars[L::bVEmpty + (i & 1)]);
       }
@@ -844,7 +893,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tmem_base + kColAcc1, ds_col + split_a_col(kk), ka + mnmajor_step(kk), kIdescTS,
+            mma_ts(tmem_base + kColAcc1, ds_col + split_a_col(kk), ka + mnmajor_step(kk), kIdescDQ,
                    kk > 0 ? 1u : first);
           mma_commit(&bars[L::bKEmpty + i % L::kKStages]);
         }
@@ -925,10 +974,24 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
 #pragma unroll
         for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
         if (p.has_bias) {
+          if (p.bias_vec && nbase + kWgCols <= sq.sk) {
+            // the thread's 32 bias values are 64 contiguous bytes: four 16-byte loads
+            const uint4* bp = reinterpret_cast<const uint4*>(bias_row + nbase);
+            uint4 w[4];
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const int n = nbase + c;
-            if (n < sq.sk) pr[c] = fmaf(to_f32<T>(bias_row[(int64_t)n * p.bias.s[3]]), kLog2e, pr[c]);
+            for (int u = 0; u < 4; ++u) w[u] = __ldg(bp + u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const T* e = reinterpret_cast<const T*>(&w[u]);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) pr[u * 8 + i] = fmaf(to_f32<T>(e[i]), kLog2e, pr[u * 8 + i]);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int n = nbase + c;
+              if (n < sq.sk) pr[c] = fmaf(to_f32<T>(bias_row[(int64_t)n * p.bias.s[3]]), kLog2e, pr[c]);
+            }
           }
         }
 #pragma unroll

@@ -78,8 +78,8 @@ struct FwdSmem {
   static constexpr int bQFull = 0 /*2*/, bKFull = 2, bKEmpty = 4, bVFull = 6, bVEmpty = 8, bSFull = 10 /*2*/,
                        bPFull = 12 /*2*/, bPvDone = 14 /*2*/, bPHalf = 16 /*2*/, bCount = 18;
   static constexpr int kTmemSlot = kBars + bCount * 8;
-  static constexpr int kAbort = kTmemSlot + 4;
-  static constexpr int kTotal = kAbort + 4;
+  static constexpr int kAbort = kTmemSlot + 4;               // abort word, then the launch's wait limit
+  static constexpr int kTotal = kAbort + 8;
   static constexpr int kDynamic = kTotal + 1024;             // slack for manual 1024-byte alignment
 };
 
@@ -111,7 +111,8 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int z = blockIdx.z, h = blockIdx.y;
   const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * kCtaRows;   // long tiles of a causal problem first
-  if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;   // an earlier CTA timed out
+  // An earlier CTA timed out: the whole CTA leaves (one read, one CTA-wide decision).
+  if (__syncthreads_or(threadIdx.x == 0 && *reinterpret_cast<volatile unsigned int*>(status) != 0u)) return;
   // One thread of the grid reports the seed and offset actually used, before any early exit.
   if (p.dropout_on && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
     uint64_t seed = p.seed_ptr ? *p.seed_ptr : 0ull;
@@ -136,7 +137,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
 
   // ---- set-up -----------------------------------------------------------------------
   if (threadIdx.x == 0) {
-    *abort_flag = 0;
+    init_abort_and_limit(abort_flag, p.wait_limit_kcycles);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars[L::bQFull + s], 1);
       mbar_init(&bars[L::bKFull + s], 1);
@@ -163,6 +164,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       mbar_expect_tx(&bars[L::bKFull + j], L::kTileBytes);
       for (int hf = 0; hf < L::kHalves; ++hf)
         tma_load_4d(smem + L::kK + j * L::kTileBytes + hf * 16384, &tm_k, &bars[L::bKFull + j], hf * 64, krow, hk, sq.bidx);
+      if (p.drop_copy == 1 && j == 0) continue;   // test hook: this block's V never arrives
       mbar_expect_tx(&bars[L::bVFull + j], L::kTileBytes);
       for (int hf = 0; hf < L::kHalves; ++hf)
         tma_load_4d(smem + L::kV + j * L::kTileBytes + hf * 16384, &tm_v, &bars[L::bVFull + j], hf * 64, krow, hk, sq.bidx);
@@ -202,11 +204,12 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         }
         if (*abort_flag) {
           // Let copies that are still in flight land before the CTA gives its shared memory back.
-          for (int t = 0; t < ntile; ++t) mbar_wait_quiet(&bars[L::bQFull + t], 0);
+          for (int t = 0; t < ntile; ++t) mbar_wait_quiet(&bars[L::bQFull + t], 0, abort_flag);
           for (int i = max(0, issued - 2 * kStages); i < issued; ++i) {
             int j = i >> 1, s = j % kStages;
             uint32_t ph = (uint32_t)(j / kStages) & 1u;
-            mbar_wait_quiet((i & 1) ? &bars[L::bVFull + s] : &bars[L::bKFull + s], ph);
+            if (p.drop_copy == 1 && i == 1) continue;   // (never issued)
+            mbar_wait_quiet((i & 1) ? &bars[L::bVFull + s] : &bars[L::bKFull + s], ph, abort_flag);
           }
         }
       }
@@ -215,8 +218,12 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       // ================================ MMA issuer ====================================
       // The whole warp walks the loop and waits; one elected lane issues.  With warp-uniform
       // control flow the descriptors stay in uniform registers and a GEMM costs few issue slots.
+      // The contraction of Q K^T runs over the head dimension rounded up to 16 and P V produces the
+      // value head dimension rounded up to 16 (the copies zero-fill up to the 64-column box), so a
+      // padded head dimension costs its own size, not the kernel's.
       constexpr uint32_t kIdescQK = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
-      constexpr uint32_t kIdescPV = instr_desc_f16(Fmt<T>::code, 128, HD, 0, 1);
+      const uint32_t kIdescPV = instr_desc_f16(Fmt<T>::code, 128, (uint32_t)((p.dvo + 15) & ~15), 0, 1);
+      const int ksteps = (p.dqk + 15) >> 4;
       // Descriptors are built once; a k-step, a tile or a ring stage only moves the 14-bit
       // start-address field (units of 16 bytes), which cannot carry out of the field.
       const uint64_t q_desc = smem_desc_sw128(smem_u32(smem + L::kQ), 16, 1024);
@@ -235,7 +242,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
           for (int kk = 0; kk < HD / 16; ++kk) {
             constexpr uint32_t kHalfStep = 16384u >> 4, kInner = 32u >> 4;
             const uint32_t off = (uint32_t)(kk >> 2) * kHalfStep + (uint32_t)(kk & 3) * kInner;
-            mma_ss(tmem_base + (uint32_t)t * 128u, qd + off, kd + off, kIdescQK, kk > 0 ? 1u : 0u);
+            if (kk < ksteps) mma_ss(tmem_base + (uint32_t)t * 128u, qd + off, kd + off, kIdescQK, kk > 0 ? 1u : 0u);
           }
           mma_commit(&bars[L::bSFull + t]);
           if (release_k) mma_commit(&bars[L::bKEmpty + (j % kStages)]);
@@ -253,6 +260,9 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         const int s = j % kStages;
         const uint32_t par = (uint32_t)j & 1u;
         if (!wait(L::bVFull + s, (uint32_t)(j / kStages) & 1u, 0x600 + j)) break;
+        // Last, partial block of the sequence: the rows of V beyond its end must not reach P V.
+        if ((jb_lo + j + 1) * kBN > sq.sk)
+          zero_tail_rows(smem + L::kV + s * L::kTileBytes, sq.sk - (jb_lo + j) * kBN, L::kHalves, lane);
         if (j + 1 < nblk) {
           if (!wait(L::bKFull + ((j + 1) % kStages), (uint32_t)((j + 1) / kStages) & 1u, 0x400 + j + 1)) break;
         }
@@ -359,9 +369,26 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         for (int c = 0; c < 128; ++c) sc[c] *= p.qk_scale;
         if (p.has_bias) {
           const int nmax = sq.sk - n0;
+          if (p.bias_vec && nmax >= kBN) {
+            // the thread's 128 bias values are 256 contiguous bytes: sixteen 16-byte loads, four in flight
+            const uint4* bp = reinterpret_cast<const uint4*>(bias_row + n0);
 #pragma unroll
-          for (int c = 0; c < 128; ++c)
-            if (c < nmax) sc[c] = fmaf(to_f32<T>(bias_row[(int64_t)(n0 + c) * p.bias.s[3]]), kLog2e, sc[c]);
+            for (int g = 0; g < 16; g += 4) {
+              uint4 w[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) w[u] = __ldg(bp + g + u);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const T* e = reinterpret_cast<const T*>(&w[u]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sc[(g + u) * 8 + i] = fmaf(to_f32<T>(e[i]), kLog2e, sc[(g + u) * 8 + i]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 128; ++c)
+              if (c < nmax) sc[c] = fmaf(to_f32<T>(bias_row[(int64_t)(n0 + c) * p.bias.s[3]]), kLog2e, sc[c]);
+          }
         }
         if (any_mask) {
 #pragma unroll
@@ -392,6 +419,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
+          if (c * 32 >= p.dvo) break;          // columns the P V product never writes
           uint32_t o[32];
           tmem_ld32(o_addr + c * 32, o);
           tmem_wait_ld();
@@ -478,6 +506,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
       uint8_t* stage = smem + L::kQ + t * L::kTileBytes;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
+        if (c * 32 >= p.dvo) break;
         float o[32];
         tmem_ld32f(o_addr + c * 32, o);
         tmem_wait_ld();

@@ -55,10 +55,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr long long kWaitLimitCycles = 2000000000ll;
 constexpr int kSpinsPerCheck = 64;
 
+// The CTA's abort word is followed by the wait limit of this launch in units of 1024 cycles
+// (0 = kWaitLimitCycles); the thread that initialises the barriers writes both.
+__device__ __forceinline__ void init_abort_and_limit(volatile uint32_t* abort_flag, uint32_t limit_kcycles) {
+  abort_flag[0] = 0u;
+  abort_flag[1] = limit_kcycles;
+}
+__device__ __forceinline__ long long wait_limit_cycles(volatile uint32_t* abort_flag) {
+  const uint32_t k = abort_flag[1];
+  return k != 0u ? (long long)k * 1024ll : kWaitLimitCycles;
+}
+
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           unsigned int* status, uint32_t where) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  const long long limit = wait_limit_cycles(abort_flag);
   for (;;) {
     // The polling loop proper is two instructions; the abort flag and the clock are looked at once
     // in kSpinsPerCheck polls.  (Waiting warps share their scheduler's issue slots with the warps
@@ -73,7 +85,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 #endif
       return false;
     }
-    if (clock64() - t0 > kWaitLimitCycles) break;
+    if (clock64() - t0 > limit) break;
   }
 #ifdef AB200_DEBUG_WAITS
   if ((threadIdx.x & 31) == 0) printf("blk %d,%d,%d warp %d TIMEOUT at %x\n", blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x >> 5, where);
@@ -89,6 +101,7 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
                                                   unsigned int* status, uint32_t where) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  const long long limit = wait_limit_cycles(abort_flag);
   for (;;) {
 #pragma unroll 1
     for (int spin = 0; spin < kSpinsPerCheck; ++spin) {
@@ -96,7 +109,7 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
       __nanosleep(200);
     }
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) break;
+    if (clock64() - t0 > limit) break;
   }
   *abort_flag = 1u;
   if (status) atomicCAS(status, 0u, where);
@@ -104,10 +117,11 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
 }
 
 // Bounded wait without side effects, for draining copies on the failure path.
-__device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
   const long long t0 = clock64();
+  const long long limit = wait_limit_cycles(abort_flag);
   while (!mbar_try_wait(bar, parity))
-    if (clock64() - t0 > kWaitLimitCycles) return;
+    if (clock64() - t0 > limit) return;
 }
 
 // Packed pairs of fp32 operations (one instruction for two lanes of work on sm_100).
@@ -170,6 +184,22 @@ __device__ __forceinline__ float ex2(float x) {
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// Warp-collective: zero rows [valid_rows, 128) of a [128 rows x 64*halves columns] 16-bit tile in
+// the TMA tile layout (row r of 64-column half hf at hf*16384 + r*128; the 128-byte swizzle only
+// permutes 16-byte chunks inside a row), then make the writes visible to the tensor core.  Used on
+// the last, partial block of a sequence: the bulk copy is bounded by the tensor, not by the
+// sequence, so the rows beyond the sequence's end hold a neighbour's tokens or padding, and a zero
+// probability times a non-finite value there would poison the product (the reference zero-fills
+// such rows with masked loads, modules/flash/kernel/masked_load_store.py:214-307).
+__device__ __forceinline__ void zero_tail_rows(uint8_t* tile, int valid_rows, int halves, int lane) {
+  const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+  for (int hf = 0; hf < halves; ++hf)
+    for (int o = valid_rows * 128 + lane * 16; o < 16384; o += 512)
+      *reinterpret_cast<uint4*>(tile + hf * 16384 + o) = z;
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

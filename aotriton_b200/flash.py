@@ -170,13 +170,41 @@ def debug_simulate_encoded_softmax(R, dropout_p, philox_seed, philox_offset1, ph
 
 
 def lazy_dq_acc(dq: torch.Tensor):
-    return _p.lazy_tensor.dq_acc(T4(dq.data_ptr(), tuple(dq.size()), tuple(dq.stride()), cast_dtype(dq.dtype)),
-                                 dq.device.index)
+    """fp32 zero-initialised dQ accumulator shaped like dq, allocated by torch only if the backward
+    asks for it (reference: bindings/lazy_tensor/lazy_tensor_template.h:19-58, at::zeros)."""
+    like = T4(dq.data_ptr(), tuple(dq.size()), tuple(dq.stride()), cast_dtype(dq.dtype))
+    return _p.lazy_tensor.dq_acc_from(like, lambda: torch.zeros(dq.shape, dtype=torch.float32, device=dq.device))
 
 
 def lazy_delta(L: torch.Tensor):
-    return _p.lazy_tensor.delta(T2(L.data_ptr(), tuple(L.size()), tuple(L.stride()), cast_dtype(L.dtype)),
-                                L.device.index)
+    """fp32 delta scratch shaped like the logsumexp tensor, allocated by torch when the backward
+    acquires it (reference: lazy_tensor_template.h:60-97, at::empty)."""
+    like = T2(L.data_ptr(), tuple(L.size()), tuple(L.stride()), cast_dtype(L.dtype))
+    return _p.lazy_tensor.delta_from(like, lambda: torch.empty(L.shape, dtype=torch.float32, device=L.device))
+
+
+def pooled_lazy_delta(L: torch.Tensor):
+    """The same from the module's own cudaMalloc pool (no torch allocator involved), bound to the
+    current stream."""
+    like = T2(L.data_ptr(), tuple(L.size()), tuple(L.stride()), cast_dtype(L.dtype))
+    return _p.lazy_tensor.delta(like, L.device.index, torch.cuda.current_stream().cuda_stream)
+
+
+def pooled_lazy_dq_acc(dq: torch.Tensor):
+    like = T4(dq.data_ptr(), tuple(dq.size()), tuple(dq.stride()), cast_dtype(dq.dtype))
+    return _p.lazy_tensor.dq_acc(like, dq.device.index, torch.cuda.current_stream().cuda_stream)
+
+
+def check_stream():
+    """Synchronise the current stream and raise if a kernel of this library gave up on a bounded
+    wait (its outputs are then incomplete).  The condition is sticky until reset_kernel_status()."""
+    err = _p.stream_check(_stream())
+    if err != hipError_t.hipSuccess:
+        raise RuntimeError(f"aotriton_b200: stream check failed: {err} (kernel status {_p.kernel_status(False):#x})")
+
+
+def reset_kernel_status():
+    return _p.kernel_status(True)
 
 
 def eager_delta(delta: torch.Tensor):

@@ -136,7 +136,10 @@ AB200_API int ab200_attn_bwd(const ab200_attn_bwd_args* args, void* stream);
  *   - Limit: the logsumexp/delta matrix of the call (batch * num_head_q * max_seqlen_q
  *     floats; for token-packed varlen num_head_q * q.size[2]) must fit in the array,
  *     otherwise the call returns hipErrorInvalidValue (1), prints one line naming the limit
- *     to stderr, and launches nothing.
+ *     to stderr, and launches nothing.  For token-packed varlen q.size[2] must be the packed
+ *     token count, i.e. at least cu_seqlens_q[batch] (seq_strides_q[batch] for strided
+ *     varlen): the kernels index delta up to that count, which only the device knows, so a
+ *     packed call with q.size[2] <= 0 is refused as well.
  *   - The first call on each device looks up the array's device address; make that call
  *     with the device current and before any stream capture begins.  Later calls only launch.
  *   - Nothing is allocated or freed here, by the CUDA runtime or any other library.
@@ -187,6 +190,25 @@ AB200_API int ab200_last_bwd_family(void);
  * second, record where, and exit).  Synchronises the device.  reset != 0 clears the word.
  * The reference has no counterpart: its kernels contain no waits. */
 AB200_API unsigned int ab200_kernel_status(int reset);
+
+/* Synchronises `stream` and reports its device's health: 0, a CUDA error number, or
+ * hipErrorLaunchFailure (719) when a kernel gave up on a bounded wait (ab200_kernel_status
+ * then names the wait).  The health word is sticky: after a failure every CTA of every later
+ * tcgen05 launch on that device returns at once WITHOUT writing its outputs, and once this
+ * function or ab200_kernel_status has seen the failure the entry points refuse further
+ * launches on the device with 719, until ab200_kernel_status(1) clears the word.
+ * The reference has no counterpart (its kernels cannot time out); launch errors there
+ * surface through hipGetLastError (modules/flash/tests/attn_torch_function.py:192-200). */
+AB200_API int ab200_stream_check(void* stream);
+
+/* Test hook for the time-out path of the bounded waits; no counterpart in the reference.
+ * For the calling thread's following launches: `wait_limit_kcycles` bounds every in-kernel
+ * wait (units of 1024 SM cycles, 0 = the default of about a second) and `drop_copy` makes
+ * the producer leave out one tile copy (1 = the forward's first V block, 2 = the dK/dV
+ * kernel's first Q/dO block, 3 = the dQ kernel's first V block, 0 = none), so that a wait
+ * runs out, the kernel records which one and returns normally.  Nothing faults or hangs:
+ * the kernel takes a few limits to drain.  Call with (0, 0) to restore normal operation. */
+AB200_API void ab200_debug_bounded_wait_test(int drop_copy, unsigned int wait_limit_kcycles);
 
 /* Number of kernels launched by this library since load (all threads). */
 AB200_API uint64_t ab200_launch_count(void);

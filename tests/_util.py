@@ -69,3 +69,14 @@ def randn_inputs(shape_q, shape_k, shape_v, dtype, seed, device="cpu", dist="ran
     v = f(shape_v, generator=g, dtype=torch.float32).to(dtype)
     do = f(shape_q[:-1] + (shape_v[-1],), generator=g, dtype=torch.float32).to(dtype)
     return tuple(t.to(device) for t in (q, k, v, do))
+
+
+def expected_family(dtype, d_qk: int, d_vo: int, which: str = "fwd") -> int:
+    """Kernel family the automatic choice must take for freshly allocated (16-byte aligned, unit inner
+    stride) tensors: 2 = tcgen05 whenever the shape is inside those kernels' range, 1 = general."""
+    if dtype not in (torch.float16, torch.bfloat16):
+        return 1
+    dmax = 128
+    if d_qk > dmax or d_vo > dmax or d_qk % 8 or d_vo % 8:
+        return 1
+    return 2

@@ -10,7 +10,7 @@ import torch
 
 from oracle import attention as A
 from oracle import philox
-from _util import ATOL, LSE_ATOL, FUDGE, load_golden, close, reference_rule, randn_inputs
+from _util import ATOL, LSE_ATOL, FUDGE, load_golden, close, reference_rule, randn_inputs, expected_family
 
 pytestmark = pytest.mark.gpu
 
@@ -21,6 +21,17 @@ TL, BR = A.TOP_LEFT, A.BOTTOM_RIGHT
 def _runner():
     from _gpu_runner import run_fwd_bwd
     return run_fwd_bwd
+
+
+def _check_family(res, family, dt, d_qk, d_vo, tag):
+    """The automatic choice must land on the tcgen05 kernels exactly when the shape is in their range
+    (a stride or alignment regression would otherwise fall back silently and still pass parity)."""
+    want = {"general": 1, "sm100": 2}.get(family)
+    for which in ("fwd", "bwd"):
+        if which + "_family" not in res:
+            continue
+        w = want if want is not None else expected_family(dt, d_qk, d_vo, which)
+        assert res[which + "_family"] == w, f"{tag}: {which} ran on family {res[which + '_family']}, expected {w}"
 
 
 def _check(res, ref, dt, tag, keys=("out", "dq", "dk", "dv"), lse=True, scale=1.0):
@@ -43,6 +54,7 @@ def test_golden_dense(name, family):
     res = _runner()(g["q"], g["k"], g["v"], g["do"], sm_scale=g["sm_scale"], bias=g.get("b"),
                     causal_type=g["causal_type"], window_left=g["window_left"], window_right=g["window_right"],
                     family=family, want_dbias="b" in g)
+    _check_family(res, family, dt, D, Dv, name)
     for key, gk in (("out", "o"), ("dq", "dq"), ("dk", "dk"), ("dv", "dv")):
         ok, err = close(res[key].float(), g[gk].float(), ATOL[dt])
         assert ok, f"{name}:{key} max err {err}"
@@ -64,6 +76,7 @@ def test_golden_varlen(family):
     res = _runner()(g["q"], g["k"], g["v"], g["do"], sm_scale=g["sm_scale"], causal_type=g["causal_type"],
                     window_left=g["window_left"], window_right=g["window_right"], cu_q=cu_q, cu_k=cu_k,
                     max_sq=int(lens.max()), max_sk=int(lens.max()), family=family, keep_layout=thd)
+    _check_family(res, family, g["dtype"], g["q"].shape[3], g["v"].shape[3], "golden varlen")
     for key, gk in (("out", "o"), ("dq", "dq"), ("dk", "dk"), ("dv", "dv")):
         ok, err = close(res[key].float(), g[gk].float(), ATOL[g["dtype"]])
         assert ok, f"{key} max err {err}"
@@ -115,6 +128,7 @@ def test_dense_vs_oracle(case, family, dist):
     res = _runner()(q, k, v, do, sm_scale=sm, bias=bias, causal_type=ct, window_left=wl, window_right=wr,
                     dropout_p=p, seed=seed, offset1=off1, offset2=off2, family=family, want_dbias=use_bias)
     tag = f"{case}/{family}/{dist}"
+    _check_family(res, family, dt, D, Dv, tag)
     # Flat tolerances scale with the size of the reference values for unnormalised N(0,1) gradients.
     _check(res, ref, dt, tag)
     if use_bias:
@@ -157,6 +171,7 @@ def test_compact_varlen_vs_oracle(family, dt, D, Hq, Hk, p, causal):
     res = _runner()(q, k, v, do, sm_scale=sm, causal_type=ct, window_left=wl, window_right=wr, dropout_p=p,
                     seed=42, offset1=0, offset2=0, cu_q=cu, cu_k=cu, max_sq=max(lens), max_sk=max(lens),
                     family=family, keep_layout=thd)
+    _check_family(res, family, dt, D, D, "compact varlen")
     _check(res, ref, dt, f"varlen/{family}")
     ok, err = close(res["delta"], ref.delta, ATOL[dt] * 4)
     assert ok, f"delta {err}"
@@ -175,6 +190,7 @@ def test_padded_and_strided_varlen(family):
     sm = D ** -0.5
     res = _runner()(q, k, v, do, sm_scale=sm, causal_type=3, window_left=TL, window_right=TL, cu_q=cu, cu_k=cu,
                     max_sq=S, max_sk=S, family=family, varlen_type=cabi.VARLEN_PADDED)
+    _check_family(res, family, dt, D, D, "padded varlen")
     for z, L in enumerate(lens):
         ref = A.attention(q[z:z + 1, :, :L], k[z:z + 1, :, :L], v[z:z + 1, :, :L], sm_scale=sm,
                           mask=A.window_mask(L, L, 3, TL, TL), dout=do[z:z + 1, :, :L])
@@ -192,6 +208,7 @@ def test_padded_and_strided_varlen(family):
     thd = lambda t: t.transpose(1, 2).contiguous().transpose(1, 2)
     res = _runner()(q, k, v, do, sm_scale=sm, cu_q=cu, cu_k=cu, max_sq=S, max_sk=S, family=family,
                     varlen_type=cabi.VARLEN_STRIDED, seq_strides_q=starts, seq_strides_k=starts, keep_layout=thd)
+    _check_family(res, family, dt, D, D, "strided varlen")
     for z, L in enumerate(lens):
         a = starts[z]
         ref = A.attention(q[:, :, a:a + L], k[:, :, a:a + L], v[:, :, a:a + L], sm_scale=sm, dout=do[:, :, a:a + L])
@@ -212,6 +229,7 @@ def test_bshd_layout(family):
     bshd = lambda t: t.transpose(1, 2).contiguous().transpose(1, 2)
     res = _runner()(q, k, v, do, sm_scale=sm, causal_type=3, window_left=TL, window_right=TL, family=family,
                     keep_layout=bshd)
+    _check_family(res, family, dt, 128, 128, "bshd")
     _check(res, ref, dt, f"bshd/{family}")
 
 

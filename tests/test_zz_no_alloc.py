@@ -53,6 +53,52 @@ def test_static_scratch_matches_caller_scratch_twice(dt, B, Hq, Hk, S, D, causal
     assert cabi.lib().ab200_kernel_status(0) == 0
 
 
+def test_static_scratch_compact_varlen_and_no_allocation():
+    """Token-packed varlen (delta laid out as heads x packed tokens), and proof that the entry point
+    takes no device memory: free memory reported by the driver is the same before and after."""
+    import numpy as np
+    from aotriton_b200 import cabi
+    dt, Hq, Hk, D = torch.float16, 4, 2, 64
+    lens = [100, 37, 260]
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device="cuda")
+    T = int(sum(lens))
+    g = torch.Generator().manual_seed(23)
+    mk = lambda H: torch.randn(1, T, H, D, generator=g).to(dt).cuda().transpose(1, 2)
+    q, k, v, do = mk(Hq), mk(Hk), mk(Hk), mk(Hq)
+    prob = dict(sm_scale=D ** -0.5, causal_type=3, window_left=cabi.WINDOW_TOP_LEFT, window_right=cabi.WINDOW_TOP_LEFT,
+                cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens), max_seqlen_k=max(lens))
+    out = torch.empty_like(q)
+    lse = torch.empty(Hq, T, dtype=torch.float32, device="cuda")
+    assert cabi.attn_fwd(q, k, v, out, lse, **prob) == 0
+    want = _backward("all", q, k, v, out, do, lse, torch.empty_like(lse), **prob)
+    # Outputs and their snapshots are allocated up front, so that nothing inside the measured window
+    # goes through torch's allocator either.
+    outs = [torch.empty_like(t) for t in (q, k, v)]
+    snaps = [[torch.empty_like(t) for t in (q, k, v)] for _ in range(2)]
+    assert cabi.attn_bwd(q, k, v, out, do, *outs, lse, None, stage="static_scratch", **prob) == 0   # symbol look-up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for call in range(2):
+        for t in outs:
+            t.fill_(float("nan"))
+        assert cabi.attn_bwd(q, k, v, out, do, *outs, lse, None, stage="static_scratch", **prob) == 0
+        for dst, src in zip(snaps[call], outs):
+            dst.copy_(src)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, f"device memory changed by {free_before - free_after} bytes"
+    for call in range(2):
+        for name, g_, w in zip(("dq", "dk", "dv"), snaps[call], want):
+            ok, err = close(g_.float().cpu(), w.float().cpu(), ATOL[dt])
+            assert ok, f"varlen call {call}: {name} differs from ab200_attn_bwd by {err}"
+    # a packed call that does not declare its token count cannot be bounded and is refused
+    a = cabi.make_bwd_args(q, k, v, out, do, *want, lse, None, **prob)
+    a.q.size[2] = 0
+    before = cabi.lib().ab200_launch_count()
+    assert cabi.lib().ab200_attn_bwd_static_scratch(C.byref(a), None) == 1
+    assert cabi.lib().ab200_launch_count() == before
+
+
 def test_static_scratch_refuses_problems_beyond_its_array():
     from aotriton_b200 import cabi
     # batch * heads * seqlen = 2 * 64 * 16384 rows > 2**20: rejected on the host, nothing launched
