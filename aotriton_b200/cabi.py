@@ -19,7 +19,8 @@ STATIC_DELTA_FLOATS = 1 << 20   # AB200_STATIC_DELTA_FLOATS
 
 # Exported symbols, in header order (checked by the CPU test-suite).
 SYMBOLS = [
-    "ab200_attn_fwd", "ab200_attn_bwd", "ab200_attn_bwd_static_scratch", "ab200_bwd_preprocess", "ab200_bwd_dkdv", "ab200_bwd_dq",
+    "ab200_attn_fwd", "ab200_attn_bwd", "ab200_attn_bwd_static_scratch", "ab200_bwd_uses_dq_acc", "ab200_bwd_fused",
+    "ab200_bwd_postprocess", "ab200_bwd_preprocess", "ab200_bwd_dkdv", "ab200_bwd_dq",
     "ab200_debug_simulate_encoded_softmax", "ab200_check_gpu", "ab200_multiprocessor_count",
     "ab200_set_kernel_family", "ab200_last_fwd_family", "ab200_last_bwd_family", "ab200_kernel_status",
     "ab200_stream_check", "ab200_debug_bounded_wait_test", "ab200_launch_count",
@@ -57,7 +58,7 @@ class BwdArgs(C.Structure):
     _fields_ = [
         ("prob", Problem), ("q", View4), ("k", View4), ("v", View4), ("bias", View4), ("out", View4),
         ("dout", View4), ("dq", View4), ("dk", View4), ("dv", View4), ("dbias", View4),
-        ("lse", C.c_void_p), ("delta", C.c_void_p), ("deterministic", C.c_int32),
+        ("lse", C.c_void_p), ("delta", C.c_void_p), ("deterministic", C.c_int32), ("dq_acc", C.c_void_p),
     ]
 
 
@@ -74,7 +75,7 @@ def lib() -> C.CDLL:
         for name in ("ab200_attn_fwd",):
             getattr(L, name).argtypes = [C.POINTER(FwdArgs), C.c_void_p]
         for name in ("ab200_attn_bwd", "ab200_attn_bwd_static_scratch", "ab200_bwd_preprocess", "ab200_bwd_dkdv",
-                     "ab200_bwd_dq"):
+                     "ab200_bwd_dq", "ab200_bwd_uses_dq_acc", "ab200_bwd_fused", "ab200_bwd_postprocess"):
             getattr(L, name).argtypes = [C.POINTER(BwdArgs), C.c_void_p]
         L.ab200_debug_simulate_encoded_softmax.argtypes = [
             C.POINTER(View4), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
@@ -158,8 +159,12 @@ def attn_fwd(q, k, v, out, lse, *, bias=None, philox_seed_output=None, philox_of
     return lib().ab200_attn_fwd(C.byref(a), stream if stream is not None else current_stream_handle())
 
 
-def make_bwd_args(q, k, v, out, dout, dq, dk, dv, lse, delta, *, bias=None, dbias=None, **problem) -> BwdArgs:
+def make_bwd_args(q, k, v, out, dout, dq, dk, dv, lse, delta, *, bias=None, dbias=None, dq_acc=None,
+                  deterministic=False, **problem) -> BwdArgs:
+    """dq_acc: optional zero-filled fp32 tensor with dq's logical shape (contiguous) for the fused form."""
     a = BwdArgs()
+    a.dq_acc = _ptr(dq_acc)
+    a.deterministic = 1 if deterministic else 0
     a.prob = make_problem(q, k, v, **problem)
     a.q, a.k, a.v, a.bias, a.out, a.dout = view4(q), view4(k), view4(v), view4(bias), view4(out), view4(dout)
     a.dq, a.dk, a.dv, a.dbias = view4(dq), view4(dk), view4(dv), view4(dbias)
@@ -170,7 +175,8 @@ def make_bwd_args(q, k, v, out, dout, dq, dk, dv, lse, delta, *, bias=None, dbia
 def attn_bwd(q, k, v, out, dout, dq, dk, dv, lse, delta, *, stream=None, stage="all", **kw) -> int:
     a = make_bwd_args(q, k, v, out, dout, dq, dk, dv, lse, delta, **kw)
     fn = {"all": "ab200_attn_bwd", "preprocess": "ab200_bwd_preprocess", "dkdv": "ab200_bwd_dkdv",
-          "dq": "ab200_bwd_dq", "static_scratch": "ab200_attn_bwd_static_scratch"}[stage]
+          "dq": "ab200_bwd_dq", "static_scratch": "ab200_attn_bwd_static_scratch", "fused": "ab200_bwd_fused",
+          "postprocess": "ab200_bwd_postprocess", "uses_dq_acc": "ab200_bwd_uses_dq_acc"}[stage]
     return getattr(lib(), fn)(C.byref(a), stream if stream is not None else current_stream_handle())
 
 

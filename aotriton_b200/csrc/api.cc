@@ -183,10 +183,17 @@ hipError_t attn_bwd(const attn_bwd_params& in, int32_t params_version, AOTRITON_
     err = hipErrorInvalidValue;
   } else {
     a.delta = static_cast<float*>(delta.data_ptr());
+    // dQ accumulator: acquired (zero-filled by the caller's allocator) only when the fused form
+    // will run, i.e. not for deterministic calls (modules/flash/csrc/attn_bwd.cc:140-154).
+    FamilyGuard guard_acc(options);
+    if (in.DQ_ACC && ab200_bwd_uses_dq_acc(&a, stream.native())) {
+      TensorView<4> acc = in.DQ_ACC.eager;
+      if (!acc && in.DQ_ACC.acquire) acc = (*in.DQ_ACC.acquire)(&in.DQ_ACC);
+      if (acc && acc.dtype() == kFloat32) a.dq_acc = static_cast<float*>(acc.data_ptr());
+    }
     log_debug("attn_bwd B=%d Hq=%d Hk=%d Sq=%d Sk=%d Dqk=%d Dvo=%d causal=%d varlen=%d p=%g", a.prob.batch,
               a.prob.num_head_q, a.prob.num_head_k, a.prob.max_seqlen_q, a.prob.max_seqlen_k, a.prob.head_dim_qk,
               a.prob.head_dim_vo, a.prob.causal_type, a.prob.varlen_type, a.prob.dropout_p);
-    FamilyGuard guard(options);
     err = static_cast<hipError_t>(ab200_attn_bwd(&a, stream.native()));
   }
   // Lazy tensors are released before returning, whatever happened (attn_bwd.cc:157-158).

@@ -301,10 +301,47 @@ int ab200_bwd_dq(const ab200_attn_bwd_args* a, void* stream) {
   return (int)launch_general(2, a->prob.dtype, p, st);
 }
 
+int ab200_bwd_uses_dq_acc(const ab200_attn_bwd_args* a, void* stream) {
+  if (a == nullptr || a->deterministic || !want_sm100(g_family)) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Params p{};
+  if (fill_bwd(a, p, true) != 0 || !a->dq.ptr || !a->dk.ptr || !a->dv.ptr) return 0;
+  if (check_device(st) != 0) return 0;
+  return sm100_bwd_fused_supported(a->prob.dtype, p) ? 1 : 0;
+}
+
+int ab200_bwd_fused(const ab200_attn_bwd_args* a, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Params p{};
+  if (int e = fill_bwd(a, p, true)) return e;
+  if (!a->dq.ptr || !a->dk.ptr || !a->dv.ptr || !a->dq_acc) return kErrInvalidValue;
+  if (int e = check_device(st)) return e;
+  DeviceGuard guard(st);
+  if (!want_sm100(g_family) || !sm100_bwd_fused_supported(a->prob.dtype, p)) return kErrNotSupported;
+  t_last_bwd = 3;
+  return (int)launch_sm100_bwd_fused(a->prob.dtype, p, a->dq_acc, st);
+}
+
+int ab200_bwd_postprocess(const ab200_attn_bwd_args* a, void* stream) {
+  if (a == nullptr || !a->dq.ptr || !a->dq_acc) return kErrInvalidValue;
+  if (a->prob.dtype < AB200_DTYPE_FP32 || a->prob.dtype > AB200_DTYPE_BF16) return kErrNotSupported;
+  if (!inner_contiguous(a->dq)) return kErrInvalidValue;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int e = check_device(st)) return e;
+  DeviceGuard guard(st);
+  View4 dq = to_view(a->dq);
+  dq.n[3] = a->prob.head_dim_qk;
+  return (int)launch_postprocess(a->prob.dtype, dq, a->dq_acc, a->prob.sm_scale, st);
+}
+
 int ab200_attn_bwd(const ab200_attn_bwd_args* a, void* stream) {
   if (a == nullptr) return kErrInvalidValue;
   if (!a->dq.ptr || !a->dk.ptr || !a->dv.ptr) return kErrInvalidValue;
   if (int e = ab200_bwd_preprocess(a, stream)) return e;
+  if (a->dq_acc != nullptr && ab200_bwd_uses_dq_acc(a, stream)) {
+    if (int e = ab200_bwd_fused(a, stream)) return e;
+    return ab200_bwd_postprocess(a, stream);
+  }
   if (int e = ab200_bwd_dkdv(a, stream)) return e;
   return ab200_bwd_dq(a, stream);
 }

@@ -433,6 +433,38 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const __grid_consta
 }
 
 // ---------------------------------------------------------------------------
+// dQ = cast(sm_scale * accumulator): the conversion that follows the fused backward, whose dQ partials
+// were summed in fp32 (ROCm/aotriton modules/flash/kernel/bwd_postprocess.py:14-84).  The
+// accumulator is contiguous in dQ's logical (batch, head, token, head-dim) order; dQ has its own
+// strides.  HBM-bound: 4 bytes read and 2 written per element.  One thread per 8 elements when the
+// rows allow 16-byte stores.  grid = (cdiv(tokens * D / 8, 256), H, B)
+template <typename T>
+__global__ void __launch_bounds__(256) bwd_postprocess_kernel(View4 dq, const float* __restrict__ acc, float scale,
+                                                              int vec) {
+  const int64_t tokens = dq.n[2], d = dq.n[3];
+  const int b = blockIdx.z, h = blockIdx.y;
+  const float* src = acc + ((int64_t)b * dq.n[1] + h) * tokens * d;
+  T* dst = reinterpret_cast<T*>(dq.ptr) + (int64_t)b * dq.s[0] + (int64_t)h * dq.s[1];
+  const int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 8;
+  if (i >= tokens * d) return;
+  if (vec) {
+    const int64_t row = i / d, col = i - row * d;      // d % 8 == 0: the 8 elements share a row
+    const float4 lo = __ldcs(reinterpret_cast<const float4*>(src + i));
+    const float4 hi = __ldcs(reinterpret_cast<const float4*>(src + i + 4));
+    const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    union { uint4 u; T e[8]; } w;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) w.e[k] = from_f32<T>(v[k] * scale);
+    *reinterpret_cast<uint4*>(dst + row * dq.s[2] + col) = w.u;
+  } else {
+    for (int k = 0; k < 8 && i + k < tokens * d; ++k) {
+      const int64_t row = (i + k) / d, col = (i + k) - row * d;
+      dst[row * dq.s[2] + col] = from_f32<T>(src[i + k] * scale);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // r[z,h,m,n] = keep ? +0.5 : -0.5 over the whole rows x cols rectangle.
 // One thread per (row, 4 columns) = one Philox counter.  grid = (cdiv(cols/4 * rows, 256), H, B)
 template <typename T>
@@ -519,6 +551,24 @@ cudaError_t launch_preprocess(int dtype, const Params& p, cudaStream_t st) {
     case 1: bwd_preprocess_kernel<float><<<grid, 256, 0, st>>>(p); break;
     case 2: bwd_preprocess_kernel<__half><<<grid, 256, 0, st>>>(p); break;
     case 3: bwd_preprocess_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p); break;
+    default: return cudaErrorInvalidValue;
+  }
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_postprocess(int dtype, const View4& dq, const float* acc, float scale, cudaStream_t st) {
+  if (dq.ptr == nullptr || acc == nullptr) return cudaErrorInvalidValue;
+  if (dq.n[0] <= 0 || dq.n[1] <= 0 || dq.n[2] <= 0 || dq.n[3] <= 0) return cudaSuccess;
+  const int64_t per = dq.n[2] * dq.n[3];
+  dim3 grid((unsigned)((per / 8 + 256) / 256), (unsigned)dq.n[1], (unsigned)dq.n[0]);
+  const int vec = (dtype != 1) && dq.n[3] % 8 == 0 && (reinterpret_cast<uintptr_t>(dq.ptr) & 15u) == 0 &&
+                  dq.s[0] % 8 == 0 && dq.s[1] % 8 == 0 && dq.s[2] % 8 == 0 && dq.s[3] == 1 &&
+                  (reinterpret_cast<uintptr_t>(acc) & 15u) == 0;
+  switch (dtype) {
+    case 1: bwd_postprocess_kernel<float><<<grid, 256, 0, st>>>(dq, acc, scale, 0); break;
+    case 2: bwd_postprocess_kernel<__half><<<grid, 256, 0, st>>>(dq, acc, scale, vec); break;
+    case 3: bwd_postprocess_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(dq, acc, scale, vec); break;
     default: return cudaErrorInvalidValue;
   }
   count_launch();

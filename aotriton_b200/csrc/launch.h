@@ -35,6 +35,11 @@ cudaError_t launch_sm100_fwd(int dtype, const Params& p, cudaStream_t st);
 bool sm100_bwd_supported(int dtype, const Params& p);
 cudaError_t launch_sm100_bwd_dkdv(int dtype, const Params& p, cudaStream_t st);
 cudaError_t launch_sm100_bwd_dq(int dtype, const Params& p, cudaStream_t st);
+// Fused backward: dK, dV and the dQ partials in one kernel (partials added to the fp32 accumulator
+// `dq_acc`, zero on entry, contiguous in dQ's logical order), then dQ = cast(sm_scale * dq_acc).
+bool sm100_bwd_fused_supported(int dtype, const Params& p);
+cudaError_t launch_sm100_bwd_fused(int dtype, const Params& p, float* dq_acc, cudaStream_t st);
+cudaError_t launch_postprocess(int dtype, const View4& dq, const float* acc, float scale, cudaStream_t st);
 // Words the tcgen05 kernels of the current device set when a bounded wait ran out (0 = none).
 // Reading synchronises the device.
 unsigned int sm100_fwd_status(bool reset);

@@ -39,6 +39,19 @@
 //   dV += cast(keep ? P/(1-p) : 0)^T dO;  dK += cast(dS)^T Q;  dQ += cast(dS) K;  dB = cast(dS);
 //   dK and dQ are multiplied by sm_scale at the end.
 //
+// The dK/dV kernel has a second form (FUSED) that also produces dQ, so that the backward runs the
+// five GEMMs it is counted with instead of seven: per query block it forms the partial
+// dQ^T = K^T dS^T (head dim x queries, keys contracted), which the compute warps -- idle at that
+// point, waiting for the next S^T -- add to a zero-initialised fp32 accumulator with
+// red.global.add (lane = head-dim index: 128 contiguous bytes per instruction); a conversion kernel (general_kernels.cu)
+// then scales and casts the accumulator into dQ.  This is the reference's DQ_ACC / bwd_postprocess
+// path (include/aotriton/flash.h:40,170, modules/flash/kernel/bwd_postprocess.py:14-84); the sum
+// order of the atomics is not fixed, so it is used only when attn_options::deterministic is false.
+// In that form dS^T goes to shared memory (the tile the write-out staging uses between items): it is
+// the A operand of dK (K-major) and the B operand of dQ^T (N-major) from the same bytes, and the
+// dQ^T partial takes the tensor-memory columns of dP^T / P^T once dV has consumed P^T.
+//   order on the tensor pipe:  dV_i  dQ^T_i  S^T_{i+1}  dK_i  dP^T_{i+1}   (dQ^T_i is added out under S^T_{i+1}, dK_i)
+//
 // Every wait is bounded (sm100_ptx.cuh).
 #include <atomic>
 #include "launch.h"
@@ -83,6 +96,7 @@ using namespace ptx;
 
 constexpr int kBlk = 128;
 constexpr int kBwdThreads = 640;
+constexpr int kFusedThreads = kBwdThreads;
 constexpr int kComputeWarps = 16;      // warps 4..19; each arrives on the hand-off barriers once (lane 0)
 constexpr int kWgCols = 32;            // score columns per compute warpgroup
 constexpr uint32_t kTmemCols = 512;
@@ -101,8 +115,8 @@ struct BwdSmem {
   static constexpr int kBars = kSched + 16;
   static constexpr int bResFull = 0, bRingFull = 1, bRingEmpty = 3, bSFull = 5 /* two */, bAuxEmpty = 7,
                        bDpFull = 10 /* two: one per dP buffer in the dQ kernel */, bDsFull = 12, bAccDone = 13, bSRead = 14,
-                       bResEmpty = 15, bPFull = 16, bSchedFull = 17, bSchedEmpty = 19,
-                       bCount = 21;
+                       bResEmpty = 15, bPFull = 16, bSchedFull = 17, bSchedEmpty = 19, bDqFull = 21, bDqRead = 22,
+                       bStageFree = 23, bCount = 24;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;           // abort word, then the launch's wait limit
   static constexpr int kUsed = kAbort + 8;
@@ -163,6 +177,9 @@ __device__ __forceinline__ void init_barriers(uint64_t* bars, volatile uint32_t*
     mbar_init(&bars[L::bSchedFull + s], 1);
     mbar_init(&bars[L::bSchedEmpty + s], kComputeWarps + 3);   // compute warps, producer, MMA issuer, aux warp
   }
+  mbar_init(&bars[L::bDqFull], 1);
+  mbar_init(&bars[L::bDqRead], kComputeWarps);
+  mbar_init(&bars[L::bStageFree], kComputeWarps);
   mbar_init(&bars[L::bDpFull], 1);
   mbar_init(&bars[L::bDpFull + 1], 1);
   mbar_init(&bars[L::bDsFull], kComputeWarps);
@@ -211,12 +228,12 @@ __device__ __forceinline__ DkdvItem dkdv_item(const Params& p, int w) {
   return it;
 }
 
-template <typename T, int HD>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+template <typename T, int HD, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? kFusedThreads : kBwdThreads, 1)
 sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const __grid_constant__ CUtensorMap tm_do, unsigned int* status, int nitems,
-                      unsigned int* ticket) {
+                      unsigned int* ticket, float* dq_acc) {
   using L = BwdSmem<HD>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -264,7 +281,6 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-
   if (warp == 0) {
     // ================================ TMA producer ===================================
     if (lane == 0) {
@@ -322,6 +338,11 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     const uint64_t k_km = kmajor_base(smem_u32(smem + L::kResA)), v_km = kmajor_base(smem_u32(smem + L::kResB));
     const uint64_t q_km = kmajor_base(smem_u32(smem + L::kRingA)), do_km = kmajor_base(smem_u32(smem + L::kRingB));
     const uint64_t q_mn = mnmajor_base(smem_u32(smem + L::kRingA)), do_mn = mnmajor_base(smem_u32(smem + L::kRingB));
+    // fused form: K as the M-major A operand of dQ^T, the dS^T tile as its N-major B operand and as
+    // the K-major A operand of dK
+    const uint64_t k_mn = mnmajor_base(smem_u32(smem + L::kResA));
+    const uint64_t ds_mn = mnmajor_base(smem_u32(smem + L::kStage)), ds_km = kmajor_base(smem_u32(smem + L::kStage));
+    constexpr uint32_t kIdescDQT = instr_desc_f16(Fmt<T>::code, 128, 128, 1, 1);
     auto wait = [&](int bar, uint32_t parity, uint32_t where) {
       return __all_sync(0xffffffffu, mbar_wait(&bars[bar], parity, abort_flag, status, where)) != 0;
     };
@@ -357,6 +378,13 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       // first iteration of the item: K/V resident, Q/dO block landed, S buffer read out by the
       // compute warps (the dP buffer is released in issue order by the previous item's dV/dK)
       if (!wait(L::bResFull, live & 1u, 0x1200)) break;
+      // Last, partial key block of the sequence: keys beyond its end are rows of S^T / dP^T that are
+      // never stored, but in the fused form they are contracted over by dQ^T, where a zero dS^T times
+      // a non-finite K row (or dS^T made non-finite by a V row) would poison the sum.
+      if (it.sq.sk - it.n0 < kBlk) {
+        zero_tail_rows(smem + L::kResA, it.sq.sk - it.n0, L::kHalves, lane);
+        zero_tail_rows(smem + L::kResB, it.sq.sk - it.n0, L::kHalves, lane);
+      }
       if (G > 0 && !wait(L::bSRead, (G - 1) & 1u, 0x1201)) break;
       if (!wait(L::bRingFull + (G & 1u), (G >> 1) & 1u, 0x1202)) break;
       if (lane == 0) AB200_STAMP(G, 15);
@@ -372,12 +400,16 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       zero_ring_tail(G, 0);
       tc_fence_after();
       issue_s(G);
-      issue_dp(G, it.niter == 1);
+      if constexpr (FUSED) {      // the previous iteration's dQ^T partial has left the dP columns
+        if (G > 0 && !wait(L::bDqRead, (G - 1) & 1u, 0x1203)) break;
+        tc_fence_after();
+      }
+      issue_dp(G, !FUSED && it.niter == 1);
       if (lane == 0) AB200_STAMP(G, 8);
       for (int i = 0, mb_next = 1; i < it.niter; ++i, ++G, ++mb_next) {     // mb_next: (i + 1) % nmb
         const uint32_t s = G & 1u, par = G & 1u;
         if (mb_next == it.nmb) mb_next = 0;
-        if (i + 1 < it.niter) {
+        if (!FUSED && i + 1 < it.niter) {
           // S_g sits in registers of every compute thread: its buffer can take S_{g+1} already.
           if (!wait(L::bSRead, par, 0x1300)) { ok = false; break; }
           if (!wait(L::bRingFull + ((G + 1) & 1u), ((G + 1) >> 1) & 1u, 0x1400)) { ok = false; break; }
@@ -400,17 +432,56 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         if (!wait(L::bDsFull, par, 0x1500)) { ok = false; break; }
         if (lane == 0) AB200_STAMP(G, 5);
         tc_fence_after();
-        if (elect_one()) {   // dK += dS^T Q_g  (dS^T: the next 16 packed columns)
-          const uint64_t qa = q_mn + (uint64_t)(s * kStageStep);
+        if constexpr (FUSED) {
+          if (elect_one()) {
+            // dQ^T_g = K^T dS^T_g into the dP columns (dV, issued above, has consumed P^T there);
+            // both operands in shared memory, keys contracted in 8 steps of 16
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + 16u + split_a_col(kk), qa + mnmajor_step(kk), kIdescDK,
-                   kk > 0 ? 1u : first);
-          mma_commit(&bars[L::bRingEmpty + s]);
-          if (i + 1 == it.niter) mma_commit(&bars[L::bAccDone]);
+            for (int kk = 0; kk < 8; ++kk)
+              mma_ss(tmem_base + kColDP, k_mn + mnmajor_step(kk), ds_mn + mnmajor_step(kk), kIdescDQT, kk > 0 ? 1u : 0u);
+            mma_commit(&bars[L::bDqFull]);
+          }
+          __syncwarp();
+          if (i + 1 < it.niter) {
+            // S^T_{g+1} goes between dQ^T_g and dK_g: the adders then have two GEMMs' time to take the
+            // partial out of tensor memory before dP^T_{g+1} needs its columns.
+            if (!wait(L::bSRead, par, 0x1300)) { ok = false; break; }
+            if (!wait(L::bRingFull + ((G + 1) & 1u), ((G + 1) >> 1) & 1u, 0x1400)) { ok = false; break; }
+            zero_ring_tail(G + 1, mb_next);
+            tc_fence_after();
+            issue_s(G + 1);
+          }
+          if (elect_one()) {
+            // dK += dS^T Q_g  (dS^T from shared memory, K-major)
+            const uint64_t qa = q_mn + (uint64_t)(s * kStageStep);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+              mma_ss(tmem_base + kColAcc1, ds_km + kmajor_step(kk), qa + mnmajor_step(kk), kIdescDK, kk > 0 ? 1u : first);
+            mma_commit(&bars[L::bRingEmpty + s]);
+            if (i + 1 == it.niter) {
+              mma_commit(&bars[L::bAccDone]);
+              mma_commit(&bars[L::bResEmpty]);     // K was still being read by dQ^T
+            }
+          }
+          __syncwarp();
+          if (i + 1 < it.niter) {
+            if (!wait(L::bDqRead, par, 0x1580)) { ok = false; break; }
+            tc_fence_after();
+            issue_dp(G + 1, false);
+          }
+        } else {
+          if (elect_one()) {   // dK += dS^T Q_g  (dS^T: the next 16 packed columns)
+            const uint64_t qa = q_mn + (uint64_t)(s * kStageStep);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)
+              mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + 16u + split_a_col(kk), qa + mnmajor_step(kk), kIdescDK,
+                     kk > 0 ? 1u : first);
+            mma_commit(&bars[L::bRingEmpty + s]);
+            if (i + 1 == it.niter) mma_commit(&bars[L::bAccDone]);
+          }
+          __syncwarp();
+          if (i + 1 < it.niter) issue_dp(G + 1, i + 2 == it.niter);
         }
-        __syncwarp();
-        if (i + 1 < it.niter) issue_dp(G + 1, i + 2 == it.niter);
       }
       if (!ok) break;
       ++live;
@@ -629,10 +700,24 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
             pk[2 * c4] = pack2<T>(a.x, a.y);
             pk[2 * c4 + 1] = pack2<T>(b.x, b.y);
           }
-          tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16, pk);
+          if constexpr (FUSED) {
+            if (i == 0 && live > 0 &&
+                !mbar_wait(&bars[L::bStageFree], (live - 1) & 1u, abort_flag, status, 0x1E00)) { ok = false; break; }
+            // dS^T of this key row, query columns cbase..cbase+31, into the shared-memory tile both dK
+            // and dQ^T read: 64-column half wg >> 1, row r, four 16-byte chunks at (wg & 1) * 4,
+            // swizzled like a TMA tile (chunk ^ (row & 7)); conflict-free across the warp's rows.
+            uint8_t* row = smem + L::kStage + (wg >> 1) * 16384 + r * 128;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(row + (((((wg & 1) << 2) + j) ^ (r & 7)) << 4)) =
+                  make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+            fence_proxy_async_smem();
+          } else {
+            tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16, pk);
+          }
         }
         if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 11);
-        tmem_wait_st();
+        if constexpr (!FUSED) tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
@@ -640,6 +725,34 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           mbar_arrive(&bars[L::bAuxEmpty + s]);
         }
         if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 3);
+        if constexpr (FUSED) {
+          // dQ^T_g (head dim x queries) arrives in the dP columns two GEMMs later, while this warp
+          // would only wait for S^T_{g+1}.  This thread takes head-dim row d = its TMEM lane and the
+          // 32 query columns of its warpgroup; for a fixed query the warp's lanes add to 32
+          // consecutive floats of the accumulator row.
+          if (!mbar_wait(&bars[L::bDqFull], par, abort_flag, status, 0x1D00)) { ok = false; break; }
+          tc_fence_after();
+          float dqv[32];
+          tmem_ld32f(tmem_base + lane_addr + kColDP + cbase, dqv);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[L::bDqRead]);      // the dP columns can take dP^T_{g+1}
+          // (mbase is the first query row of this thread's columns)
+          float* acc = dq_acc + (((int64_t)sq.bidx * p.hq + h) * p.dq.n[2] + sq.q0 + mbase) * p.dqk + r;
+          const int rows = sq.sq - mbase;
+          if (r < p.dqk) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+#ifndef AB200_FUSED_NO_RED
+              if (c < rows) atomicAdd(acc + (int64_t)c * p.dqk, dqv[c]);
+#else
+              if (c < rows && dqv[c] == 123456.f) acc[(int64_t)c * p.dqk] = 0.f;
+#endif
+          }
+          __syncwarp();
+          if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 12);
+        }
       }
       if (!ok) break;
       // ---- this item's dV and dK: wait for the last two GEMMs, read out, store ----
@@ -673,6 +786,12 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
                                        (sq.k0 + it.n0) * p.dk.s[2],
                             p.dk.s[2], nrows, p.dqk, quarter * 32, wg * 4, lane, HD * 2);
         __syncwarp();
+      }
+      // The staging tile is the next item's dS^T tile: no compute warp may write dS^T there while
+      // another one is still copying its rows out (waited for before the next item's first dS^T).
+      if constexpr (FUSED) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[L::bStageFree]);
       }
     }
   }
@@ -1085,34 +1204,67 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
   }
 }
 
+// which: 1 dK/dV, 2 dQ(+dBias), 3 dK/dV fused with dQ accumulation into `dq_acc` (HD == 128 only)
 template <typename T, int HD>
-cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st) {
+cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st, float* dq_acc) {
   using L = BwdSmem<HD>;
   CUtensorMap tq, tk, tv, tdo;
   if (!make_tile_map_16bit(&tq, p.q, p.dqk, p.q.n[2], kBlk) || !make_tile_map_16bit(&tk, p.k, p.dqk, p.k.n[2], kBlk) ||
       !make_tile_map_16bit(&tv, p.v, p.dvo, p.v.n[2], kBlk) ||
       !make_tile_map_16bit(&tdo, p.dout, p.dvo, p.dout.n[2], kBlk))
     return cudaErrorInvalidValue;
-  unsigned int* status = nullptr;
-  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_sm100_bwd_status);
+  // Per-device facts (addresses of the status word and the ticket pool, SM count, the shared-memory
+  // attribute of each kernel) are looked up once for the current device, which the entry points
+  // make the stream's device, and remembered.
+  struct PerDevice { std::atomic<unsigned int*> status{nullptr}, tickets{nullptr}; std::atomic<int> sms{0}; };
+  static PerDevice per_device[64];
+  static std::atomic<bool> attr_set[64][3];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  if (which == 1) {
-    e = cudaFuncSetAttribute(sm100_bwd_dkdv_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  PerDevice& pd = per_device[dev];
+  unsigned int* status = pd.status.load(std::memory_order_acquire);
+  if (status == nullptr) {
+    if ((e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_sm100_bwd_status)) != cudaSuccess) return e;
+    pd.status.store(status, std::memory_order_release);
+  }
+  auto set_smem = [&](int slot, const void* fn, int bytes) -> cudaError_t {
+    if (attr_set[dev][slot].load(std::memory_order_acquire)) return cudaSuccess;
+    cudaError_t r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (r == cudaSuccess) attr_set[dev][slot].store(true, std::memory_order_release);
+    return r;
+  };
+  if (which == 1 || which == 3) {
+    const bool fused = which == 3;
+    if (fused && HD != 128) return cudaErrorInvalidValue;
+    auto kern_split = sm100_bwd_dkdv_kernel<T, HD, false>;
+    auto kern_fused = sm100_bwd_dkdv_kernel<T, 128, true>;
+    e = fused ? set_smem(2, reinterpret_cast<const void*>(kern_fused), BwdSmem<128>::kDynamic)
+              : set_smem(0, reinterpret_cast<const void*>(kern_split), L::kDynamic);
     if (e != cudaSuccess) return e;
     const int nitems = ((p.max_sk + kBlk - 1) / kBlk) * ((p.hk * p.batch + 7) / 8) * 8;
-    int dev = 0, sms = 0;
-    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
-    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    int sms = pd.sms.load(std::memory_order_acquire);
+    if (sms == 0) {
+      if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+      pd.sms.store(sms, std::memory_order_release);
+    }
     dim3 grid(nitems < sms ? nitems : sms, 1, 1);     // persistent: one CTA per SM
     // ticket counter of this launch: one of a small pool, zeroed in stream order
     static std::atomic<unsigned int> launch_seq{0};
-    unsigned int* tickets = nullptr;
-    if ((e = cudaGetSymbolAddress(reinterpret_cast<void**>(&tickets), g_dkdv_ticket)) != cudaSuccess) return e;
+    unsigned int* tickets = pd.tickets.load(std::memory_order_acquire);
+    if (tickets == nullptr) {
+      if ((e = cudaGetSymbolAddress(reinterpret_cast<void**>(&tickets), g_dkdv_ticket)) != cudaSuccess) return e;
+      pd.tickets.store(tickets, std::memory_order_release);
+    }
     unsigned int* ticket = tickets + (launch_seq.fetch_add(1) % kTicketPool);
     if ((e = cudaMemsetAsync(ticket, 0, sizeof(unsigned int), st)) != cudaSuccess) return e;
-    sm100_bwd_dkdv_kernel<T, HD><<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status, nitems, ticket);
+    if (fused)
+      kern_fused<<<grid, kFusedThreads, BwdSmem<128>::kDynamic, st>>>(p, tq, tk, tv, tdo, status, nitems, ticket, dq_acc);
+    else
+      kern_split<<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status, nitems, ticket, nullptr);
   } else {
-    e = cudaFuncSetAttribute(sm100_bwd_dq_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<HD>::kDynamic);
+    e = set_smem(1, reinterpret_cast<const void*>(sm100_bwd_dq_kernel<T, HD>), DqSmem<HD>::kDynamic);
     if (e != cudaSuccess) return e;
     dim3 grid((p.max_sq + kBlk - 1) / kBlk, p.hq, p.batch);
     sm100_bwd_dq_kernel<T, HD><<<grid, kBwdThreads, DqSmem<HD>::kDynamic, st>>>(p, tq, tk, tv, tdo, status);
@@ -1121,10 +1273,12 @@ cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_bwd(int which, int dtype, const Params& p, cudaStream_t st) {
-  const bool small = p.dqk <= 64 && p.dvo <= 64;
-  if (dtype == 2) return small ? launch_bwd_T<__half, 64>(which, p, st) : launch_bwd_T<__half, 128>(which, p, st);
-  return small ? launch_bwd_T<__nv_bfloat16, 64>(which, p, st) : launch_bwd_T<__nv_bfloat16, 128>(which, p, st);
+cudaError_t launch_bwd(int which, int dtype, const Params& p, cudaStream_t st, float* dq_acc) {
+  const bool small = p.dqk <= 64 && p.dvo <= 64 && which != 3;
+  if (dtype == 2)
+    return small ? launch_bwd_T<__half, 64>(which, p, st, dq_acc) : launch_bwd_T<__half, 128>(which, p, st, dq_acc);
+  return small ? launch_bwd_T<__nv_bfloat16, 64>(which, p, st, dq_acc)
+               : launch_bwd_T<__nv_bfloat16, 128>(which, p, st, dq_acc);
 }
 
 }  // namespace
@@ -1142,8 +1296,20 @@ bool sm100_bwd_supported(int dtype, const Params& p) {
   return tensor_map_encoder() != nullptr;
 }
 
-cudaError_t launch_sm100_bwd_dkdv(int dtype, const Params& p, cudaStream_t st) { return launch_bwd(1, dtype, p, st); }
-cudaError_t launch_sm100_bwd_dq(int dtype, const Params& p, cudaStream_t st) { return launch_bwd(2, dtype, p, st); }
+cudaError_t launch_sm100_bwd_dkdv(int dtype, const Params& p, cudaStream_t st) { return launch_bwd(1, dtype, p, st, nullptr); }
+cudaError_t launch_sm100_bwd_dq(int dtype, const Params& p, cudaStream_t st) { return launch_bwd(2, dtype, p, st, nullptr); }
+
+// The fused form needs the accumulator's layout to follow dQ's logical shape, 128-wide tiles, and
+// no dBias (which the dQ kernel produces).
+bool sm100_bwd_fused_supported(int dtype, const Params& p) {
+  if (!sm100_bwd_supported(dtype, p)) return false;
+  if (p.has_dbias) return false;
+  if (p.dqk <= 64 && p.dvo <= 64) return false;      // the 64-wide instantiation has no fused form
+  return p.dq.ptr != nullptr;
+}
+cudaError_t launch_sm100_bwd_fused(int dtype, const Params& p, float* dq_acc, cudaStream_t st) {
+  return launch_bwd(3, dtype, p, st, dq_acc);
+}
 
 #ifdef AB200_TRACE
 extern "C" __attribute__((visibility("default"))) int ab200_debug_read_trace(long long* out, int n) {

@@ -33,6 +33,7 @@
 //
 // Every wait is bounded (sm100_ptx.cuh); on a time-out the CTA drains and exits, and the
 // word behind `status` records which wait gave up.
+#include <atomic>
 #include "launch.h"
 #include "sm100_ptx.cuh"
 
@@ -60,18 +61,24 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kBM = 128, kBN = 128, kStages = 2;
-constexpr int kCtaRows = 2 * kBM;
+constexpr int kBM = 128, kBN = 128;
 constexpr int kFwdThreads = 384;
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;
 
+// Head dims up to 128: two query tiles per CTA and two-stage K and V rings.  Head dims up to 256:
+// a tile is 64 KB, so one query tile per CTA (S in 128 and O in 256 tensor-memory columns) and one
+// stage each for K and V; the K copy of block j+1 then runs under the softmax and P V of block j,
+// the V copy under Q K^T and the softmax of block j+1.
 template <int HD>
 struct FwdSmem {
+  static constexpr int kTiles = HD > 128 ? 1 : 2;
+  static constexpr int kStages = HD > 128 ? 1 : 2;
+  static constexpr int kCtaRows = kTiles * kBM;
   static constexpr int kHalves = HD / 64;
   static constexpr int kTileBytes = kHalves * 128 * 128;     // 128 rows x HD x 2 bytes
-  static constexpr int kQ = 0;                               // two tiles
-  static constexpr int kK = kQ + 2 * kTileBytes;
+  static constexpr int kQ = 0;                               // kTiles tiles
+  static constexpr int kK = kQ + kTiles * kTileBytes;
   static constexpr int kV = kK + kStages * kTileBytes;
   static constexpr int kBars = kV + kStages * kTileBytes;
   // barrier slots (8 bytes each)
@@ -102,6 +109,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                  unsigned int* status) {
   using L = FwdSmem<HD>;
+  constexpr int kStages = L::kStages, kCtaRows = L::kCtaRows;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
@@ -109,8 +117,26 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kAbort);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int z = blockIdx.z, h = blockIdx.y;
-  const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * kCtaRows;   // long tiles of a causal problem first
+  // Order of the CTAs (the hardware starts them by linear block index): (batch, head) pairs are taken
+  // in groups of kHeadGroup; inside a group the row-tile index runs slowest, from the tile with the
+  // most key blocks of a causal problem to the one with the fewest.  The heavy tiles of a group so
+  // start together and the grid ends on light ones, while the CTAs in flight share the K/V of one
+  // group of heads, which stays resident in L2.
+#ifndef AB200_FWD_HEAD_GROUP
+#define AB200_FWD_HEAD_GROUP 16
+#endif
+  int z = blockIdx.z, h = blockIdx.y, m0 = (int)(gridDim.x - 1 - blockIdx.x) * kCtaRows;
+  if constexpr (AB200_FWD_HEAD_GROUP > 0) {
+    constexpr int kHeadGroup = AB200_FWD_HEAD_GROUP > 0 ? AB200_FWD_HEAD_GROUP : 1;
+    const int nx = (int)gridDim.x, nh = (int)gridDim.y, nhz = nh * (int)gridDim.z;
+    const int lin = (int)blockIdx.x + nx * ((int)blockIdx.y + nh * (int)blockIdx.z);
+    const int grp = lin / (kHeadGroup * nx), r = lin - grp * (kHeadGroup * nx);
+    const int gsize = min(kHeadGroup, nhz - grp * kHeadGroup);
+    const int xi = r / gsize, hz = grp * kHeadGroup + (r - xi * gsize);
+    z = hz / nh;
+    h = hz - z * nh;
+    m0 = (nx - 1 - xi) * kCtaRows;
+  }
   // An earlier CTA timed out: the whole CTA leaves (one read, one CTA-wide decision).
   if (__syncthreads_or(threadIdx.x == 0 && *reinterpret_cast<volatile unsigned int*>(status) != 0u)) return;
   // One thread of the grid reports the seed and offset actually used, before any early exit.
@@ -123,7 +149,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
   const Seq sq = resolve_seq(p, z);
   if (m0 >= sq.sq) return;
   const int hk = h / p.group;
-  const int ntile = (m0 + kBM < sq.sq) ? 2 : 1;                   // the second tile may lie beyond the sequence
+  const int ntile = (L::kTiles == 2 && m0 + kBM < sq.sq) ? 2 : 1;   // the second tile may lie beyond the sequence
 
   // Block range: the union over the CTA's rows; a tile simply sees fully masked blocks outside its own.
   int n_lo, n_hi;
@@ -442,6 +468,29 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         const int cb = half * 64;
         if (simple) {
           const float2 sc2 = make_float2(p.qk_scale, p.qk_scale), nm2 = make_float2(-m_safe, -m_safe);
+#ifndef AB200_FWD_POLY
+#define AB200_FWD_POLY 0
+#endif
+#if AB200_FWD_POLY > 0
+          if (!any_mask) {
+            // Every score of this block is unmasked for every row of the warp: one pair in
+            // AB200_FWD_POLY takes its exponentials on the FMA pipe, which otherwise idles while the
+            // special-function unit (16 results per clock and SM) paces the loop.
+#pragma unroll
+            for (int c = cb; c < cb + 64; c += 2) {
+              const float2 a = fma2(make_float2(sc[c], sc[c + 1]), sc2, nm2);
+              if (((c >> 1) % AB200_FWD_POLY) == AB200_FWD_POLY - 1) {
+                const float2 e = exp2_fma_pair(a);
+                sc[c] = e.x;
+                sc[c + 1] = e.y;
+              } else {
+                sc[c] = ex2(a.x);
+                sc[c + 1] = ex2(a.y);
+              }
+              s4[(c >> 1) & 3] = add2(s4[(c >> 1) & 3], make_float2(sc[c], sc[c + 1]));
+            }
+          } else
+#endif
 #pragma unroll
           for (int c = cb; c < cb + 64; c += 2) {
             const float2 a = fma2(make_float2(sc[c], sc[c + 1]), sc2, nm2);
@@ -538,15 +587,27 @@ cudaError_t launch_fwd_T(const Params& p, cudaStream_t st) {
   if (!make_tile_map_16bit(&tq, p.q, p.dqk, p.q.n[2], kBM) || !make_tile_map_16bit(&tk, p.k, p.dqk, p.k.n[2], kBN) ||
       !make_tile_map_16bit(&tv, p.v, p.dvo, p.v.n[2], kBN))
     return cudaErrorInvalidValue;
-  // The attribute belongs to the (function, device) pair; setting it on every launch keeps
-  // multi-device processes correct and costs microseconds.
-  cudaError_t e = cudaFuncSetAttribute(sm100_fwd_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       L::kDynamic);
+  // The shared-memory attribute belongs to the (function, device) pair and the status word's
+  // address to the device: both are looked up once per device (the current one, which the entry
+  // points make the stream's device) and remembered.
+  static std::atomic<unsigned int*> status_of[64];
+  static std::atomic<bool> attr_set[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  unsigned int* status = nullptr;
-  e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_sm100_fwd_status);
-  if (e != cudaSuccess) return e;
-  dim3 grid((p.max_sq + kCtaRows - 1) / kCtaRows, p.hq, p.batch);
+  const bool cached = dev >= 0 && dev < 64;
+  if (!cached || !attr_set[dev].load(std::memory_order_acquire)) {
+    e = cudaFuncSetAttribute(sm100_fwd_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess) return e;
+    if (cached) attr_set[dev].store(true, std::memory_order_release);
+  }
+  unsigned int* status = cached ? status_of[dev].load(std::memory_order_acquire) : nullptr;
+  if (status == nullptr) {
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_sm100_fwd_status);
+    if (e != cudaSuccess) return e;
+    if (cached) status_of[dev].store(status, std::memory_order_release);
+  }
+  dim3 grid((p.max_sq + L::kCtaRows - 1) / L::kCtaRows, p.hq, p.batch);
   sm100_fwd_kernel<T, HD><<<grid, kFwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, status);
   count_launch();
   return cudaGetLastError();
@@ -556,7 +617,7 @@ cudaError_t launch_fwd_T(const Params& p, cudaStream_t st) {
 
 bool sm100_fwd_supported(int dtype, const Params& p) {
   if (dtype != 2 && dtype != 3) return false;                    // fp16 / bf16 only
-  if (p.dqk > 128 || p.dvo > 128 || p.dqk % 8 != 0 || p.dvo % 8 != 0) return false;
+  if (p.dqk > 256 || p.dvo > 256 || p.dqk % 8 != 0 || p.dvo % 8 != 0) return false;
   if (p.max_sq <= 0 || p.max_sk <= 0 || p.batch <= 0) return false;
   if (!tma_friendly(p.q) || !tma_friendly(p.k) || !tma_friendly(p.v)) return false;
   // O is written with 16-byte vector stores
@@ -566,9 +627,12 @@ bool sm100_fwd_supported(int dtype, const Params& p) {
 }
 
 cudaError_t launch_sm100_fwd(int dtype, const Params& p, cudaStream_t st) {
-  const bool small = p.dqk <= 64 && p.dvo <= 64;
-  if (dtype == 2) return small ? launch_fwd_T<__half, 64>(p, st) : launch_fwd_T<__half, 128>(p, st);
-  return small ? launch_fwd_T<__nv_bfloat16, 64>(p, st) : launch_fwd_T<__nv_bfloat16, 128>(p, st);
+  const int dmax = p.dqk > p.dvo ? p.dqk : p.dvo;
+  if (dtype == 2)
+    return dmax <= 64 ? launch_fwd_T<__half, 64>(p, st)
+                      : (dmax <= 128 ? launch_fwd_T<__half, 128>(p, st) : launch_fwd_T<__half, 256>(p, st));
+  return dmax <= 64 ? launch_fwd_T<__nv_bfloat16, 64>(p, st)
+                    : (dmax <= 128 ? launch_fwd_T<__nv_bfloat16, 128>(p, st) : launch_fwd_T<__nv_bfloat16, 256>(p, st));
 }
 
 #ifdef AB200_TRACE

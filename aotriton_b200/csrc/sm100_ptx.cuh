@@ -70,7 +70,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
                                           unsigned int* status, uint32_t where) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  const long long limit = wait_limit_cycles(abort_flag);
   for (;;) {
     // The polling loop proper is two instructions; the abort flag and the clock are looked at once
     // in kSpinsPerCheck polls.  (Waiting warps share their scheduler's issue slots with the warps
@@ -85,7 +84,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 #endif
       return false;
     }
-    if (clock64() - t0 > limit) break;
+    // (the launch's limit is read here, once in kSpinsPerCheck polls, not ahead of the loop: every
+    // blocking wait of the pipeline passes through this function and must start polling at once)
+    if (clock64() - t0 > wait_limit_cycles(abort_flag)) break;
   }
 #ifdef AB200_DEBUG_WAITS
   if ((threadIdx.x & 31) == 0) printf("blk %d,%d,%d warp %d TIMEOUT at %x\n", blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x >> 5, where);
@@ -101,7 +102,6 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
                                                   unsigned int* status, uint32_t where) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  const long long limit = wait_limit_cycles(abort_flag);
   for (;;) {
 #pragma unroll 1
     for (int spin = 0; spin < kSpinsPerCheck; ++spin) {
@@ -109,7 +109,7 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
       __nanosleep(200);
     }
     if (*abort_flag) return false;
-    if (clock64() - t0 > limit) break;
+    if (clock64() - t0 > wait_limit_cycles(abort_flag)) break;
   }
   *abort_flag = 1u;
   if (status) atomicCAS(status, 0u, where);
@@ -178,6 +178,26 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// 2^x for a pair of finite arguments on the FMA pipe (no special-function unit): x = n + f with
+// n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3 polynomial (relative error 7.5e-5, far below
+// the 16-bit rounding the result goes through), 2^n by adding n to the exponent field.  Arguments
+// below -126 give about 1e-38 instead of 0, so this is only used where every argument belongs to an
+// unmasked score (a masked score needs an exact 0).
+__device__ __forceinline__ float2 exp2_fma_pair(float2 x) {
+  const float2 magic = make_float2(12582912.f, 12582912.f);     // 1.5 * 2^23: the sum holds round(x) in its low bits
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = add2(x, magic);
+  const float2 f = sub2(x, sub2(t, magic));
+  float2 p = fma2(f, make_float2(5.517166712e-02f, 5.517166712e-02f), make_float2(2.426111220e-01f, 2.426111220e-01f));
+  p = fma2(p, f, make_float2(6.932609858e-01f, 6.932609858e-01f));
+  p = fma2(p, f, make_float2(9.999280736e-01f, 9.999280736e-01f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return r;
 }
 
 // ---- proxies / fences -------------------------------------------------------------
@@ -303,6 +323,15 @@ __device__ __forceinline__ void tmem_ld32f(uint32_t taddr, float* r) {
         "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]),
         "=f"(r[16]), "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]),
         "=f"(r[24]), "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16f(uint32_t taddr, float* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]),
+        "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15])
       : "r"(taddr)
       : "memory");
 }

@@ -43,7 +43,9 @@ using LT4 = AOTRITON_NS::LazyTensor<4>;
 
 // Per-call knobs.  force_backend_index: -1 automatic, 0 the general kernels,
 // 1 the tcgen05 kernels (hipErrorNotSupported if the shape is outside their
-// range).  deterministic: accepted; every backward here is deterministic.
+// range).  deterministic: true keeps the two-kernel backward, whose sums have a fixed
+// order; false (the default) lets attn_bwd use DQ_ACC and the fused backward, which
+// adds dQ partials with floating-point atomics (run-to-run differences in the last bits).
 struct AOTRITON_API attn_options {
   int force_backend_index = -1;
   bool deterministic = false;

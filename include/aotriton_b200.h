@@ -112,7 +112,14 @@ typedef struct ab200_attn_bwd_args {
   ab200_view4 dq, dk, dv, dbias;    /* dbias absent or all-zero strides -> not written */
   const float* lse;                 /* as written by the forward */
   float* delta;                     /* scratch, same shape as lse (the "D" lazy tensor) */
-  int32_t deterministic;            /* attn_options::deterministic; results are always deterministic */
+  int32_t deterministic;            /* attn_options::deterministic: non-zero forbids the fused form below */
+  /* Optional fp32 dQ accumulator (the "DQ_ACC" lazy tensor, include/aotriton/flash.h:170): contiguous
+   * in dq's logical order, dq.size[0] * dq.size[1] * dq.size[2] * head_dim_qk floats, ZERO on entry
+   * (the reference's allocator callback returns zeros).  When it is given, `deterministic` is 0 and
+   * the problem qualifies (ab200_bwd_uses_dq_acc), ab200_attn_bwd runs the fused form: one kernel
+   * produces dK, dV and adds dQ partials here with atomics, a conversion kernel writes dq.  The
+   * accumulator holds the unscaled sum afterwards.  NULL selects the two-kernel form. */
+  float* dq_acc;
 } ab200_attn_bwd_args;
 
 /* Replaces aotriton::v3::flash::attn_fwd's launch (modules/flash/csrc/attn_fwd.cc:49-149). */
@@ -150,6 +157,18 @@ AB200_API int ab200_attn_bwd(const ab200_attn_bwd_args* args, void* stream);
  */
 #define AB200_STATIC_DELTA_FLOATS (1u << 20)
 AB200_API int ab200_attn_bwd_static_scratch(const ab200_attn_bwd_args* args, void* stream);
+
+/* 1 when ab200_attn_bwd would use args->dq_acc if it were given (tcgen05 kernels apply, head dim
+ * above 64, no dBias requested, deterministic == 0), else 0; lets a caller acquire the accumulator
+ * only when it is needed, as attn_bwd does with the reference's lazy tensor
+ * (modules/flash/csrc/attn_bwd.cc:140-158). */
+AB200_API int ab200_bwd_uses_dq_acc(const ab200_attn_bwd_args* args, void* stream);
+
+/* The fused form's two stages after ab200_bwd_preprocess: dK, dV and dQ partials into args->dq_acc
+ * (the reference's fused / AITER-style backward with a dq accumulator, include/aotriton/flash.h:170),
+ * then dq = cast(sm_scale * dq_acc) (modules/flash/kernel/bwd_postprocess.py:14-84). */
+AB200_API int ab200_bwd_fused(const ab200_attn_bwd_args* args, void* stream);
+AB200_API int ab200_bwd_postprocess(const ab200_attn_bwd_args* args, void* stream);
 
 /* The three backward stages one by one (modules/flash/kernel/bwd_preprocess.py:28-250,
  * bwd_kernel_dk_dv.py:48-417, bwd_kernel_dq.py:45-389). */

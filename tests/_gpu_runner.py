@@ -5,7 +5,9 @@ import torch
 
 from aotriton_b200 import cabi
 
-FAMILY = {"auto": 0, "general": 1, "sm100": 2}
+# "fused": automatic choice with a dQ accumulator supplied, so that the backward may take the fused
+# (atomic-dQ) form where it applies
+FAMILY = {"auto": 0, "general": 1, "sm100": 2, "fused": 0}
 
 
 def dev(t):
@@ -67,6 +69,8 @@ def run_fwd_bwd(q, k, v, do=None, *, sm_scale, bias=None, causal_type=0, window_
             db = torch.full_like(bd, float("nan")) if (want_dbias and bd is not None) else None
             delta = torch.full(lse_shape, float("nan"), dtype=torch.float32, device="cuda")
             bprob = dict(prob)
+            if family == "fused":      # zero-filled fp32, contiguous in dq's logical (B, H, S, D) order
+                bprob["dq_acc"] = torch.zeros(tuple(qd.shape), dtype=torch.float32, device="cuda")
             if dropout_p > 0:   # the backward consumes what the forward reported (offset2 already folded in)
                 bprob.update(philox_seed=seed_out, philox_offset1=off_out, philox_offset2=0)
             err = cabi.attn_bwd(qd, kd, vd, out, dod, dq, dk, dv, lse, delta, bias=bd, dbias=db, **bprob)

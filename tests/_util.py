@@ -71,12 +71,15 @@ def randn_inputs(shape_q, shape_k, shape_v, dtype, seed, device="cpu", dist="ran
     return tuple(t.to(device) for t in (q, k, v, do))
 
 
-def expected_family(dtype, d_qk: int, d_vo: int, which: str = "fwd") -> int:
+def expected_family(dtype, d_qk: int, d_vo: int, which: str = "fwd", fused: bool = False, dbias: bool = False) -> int:
     """Kernel family the automatic choice must take for freshly allocated (16-byte aligned, unit inner
-    stride) tensors: 2 = tcgen05 whenever the shape is inside those kernels' range, 1 = general."""
+    stride) tensors: 2 = tcgen05 whenever the shape is inside those kernels' range, 1 = general; the
+    backward reports 3 when it ran the fused form (dQ accumulator given, head dim above 64, no dBias)."""
     if dtype not in (torch.float16, torch.bfloat16):
         return 1
-    dmax = 128
+    dmax = 256 if which == "fwd" else 128      # the forward has a 256-wide instantiation, the backward not
     if d_qk > dmax or d_vo > dmax or d_qk % 8 or d_vo % 8:
         return 1
+    if which == "bwd" and fused and not dbias and (d_qk > 64 or d_vo > 64):
+        return 3
     return 2

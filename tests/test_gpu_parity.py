@@ -14,7 +14,7 @@ from _util import ATOL, LSE_ATOL, FUDGE, load_golden, close, reference_rule, ran
 
 pytestmark = pytest.mark.gpu
 
-FAMILIES = ["general", "auto"]
+FAMILIES = ["general", "auto", "fused"]
 TL, BR = A.TOP_LEFT, A.BOTTOM_RIGHT
 
 
@@ -23,14 +23,14 @@ def _runner():
     return run_fwd_bwd
 
 
-def _check_family(res, family, dt, d_qk, d_vo, tag):
+def _check_family(res, family, dt, d_qk, d_vo, tag, dbias=False):
     """The automatic choice must land on the tcgen05 kernels exactly when the shape is in their range
     (a stride or alignment regression would otherwise fall back silently and still pass parity)."""
     want = {"general": 1, "sm100": 2}.get(family)
     for which in ("fwd", "bwd"):
         if which + "_family" not in res:
             continue
-        w = want if want is not None else expected_family(dt, d_qk, d_vo, which)
+        w = want if want is not None else expected_family(dt, d_qk, d_vo, which, family == "fused", dbias)
         assert res[which + "_family"] == w, f"{tag}: {which} ran on family {res[which + '_family']}, expected {w}"
 
 
@@ -54,7 +54,7 @@ def test_golden_dense(name, family):
     res = _runner()(g["q"], g["k"], g["v"], g["do"], sm_scale=g["sm_scale"], bias=g.get("b"),
                     causal_type=g["causal_type"], window_left=g["window_left"], window_right=g["window_right"],
                     family=family, want_dbias="b" in g)
-    _check_family(res, family, dt, D, Dv, name)
+    _check_family(res, family, dt, D, Dv, name, dbias="b" in g)
     for key, gk in (("out", "o"), ("dq", "dq"), ("dk", "dk"), ("dv", "dv")):
         ok, err = close(res[key].float(), g[gk].float(), ATOL[dt])
         assert ok, f"{name}:{key} max err {err}"
@@ -128,7 +128,7 @@ def test_dense_vs_oracle(case, family, dist):
     res = _runner()(q, k, v, do, sm_scale=sm, bias=bias, causal_type=ct, window_left=wl, window_right=wr,
                     dropout_p=p, seed=seed, offset1=off1, offset2=off2, family=family, want_dbias=use_bias)
     tag = f"{case}/{family}/{dist}"
-    _check_family(res, family, dt, D, Dv, tag)
+    _check_family(res, family, dt, D, Dv, tag, dbias=use_bias)
     # Flat tolerances scale with the size of the reference values for unnormalised N(0,1) gradients.
     _check(res, ref, dt, tag)
     if use_bias:
