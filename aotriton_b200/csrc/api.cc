@@ -98,13 +98,14 @@ void fill_problem(const P& in, ab200_attn_problem& pr) {
   pr.philox_num_head_q = 0;
 }
 
-// force_backend_index: -1 automatic, 0 general kernels, 1 tcgen05 kernels.
+// force_backend_index: -1 automatic, 0 general kernels, 1 tcgen05 kernels, 2 automatic with the
+// fused (dQ accumulator) backward where it applies.
 struct FamilyGuard {
   int old_ = -1; bool active_ = false;
   explicit FamilyGuard(const v3::flash::attn_options* o) {
     if (o && o->force_backend_index >= 0) {
       active_ = true;
-      old_ = ab200_set_kernel_family(o->force_backend_index == 0 ? 1 : 2);
+      old_ = ab200_set_kernel_family(o->force_backend_index == 0 ? 1 : (o->force_backend_index == 1 ? 2 : 3));
     }
   }
   ~FamilyGuard() { if (active_) ab200_set_kernel_family(old_); }

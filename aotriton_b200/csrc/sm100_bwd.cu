@@ -47,10 +47,11 @@
 // then scales and casts the accumulator into dQ.  This is the reference's DQ_ACC / bwd_postprocess
 // path (include/aotriton/flash.h:40,170, modules/flash/kernel/bwd_postprocess.py:14-84); the sum
 // order of the atomics is not fixed, so it is used only when attn_options::deterministic is false.
-// In that form dS^T goes to shared memory (the tile the write-out staging uses between items): it is
-// the A operand of dK (K-major) and the B operand of dQ^T (N-major) from the same bytes, and the
-// dQ^T partial takes the tensor-memory columns of dP^T / P^T once dV has consumed P^T.
-//   order on the tensor pipe:  dV_i  dQ^T_i  S^T_{i+1}  dK_i  dP^T_{i+1}   (dQ^T_i is added out under S^T_{i+1}, dK_i)
+// In that form dS^T also goes to shared memory (the tile the write-out staging uses between items)
+// as the N-major B operand of dQ^T, and the dQ^T partial of iteration i takes the S^T columns once
+// the compute warps have copied S^T_{i+1} out: it runs under their first exponentials of iteration
+// i+1 and is added out between the remaining ones; S^T_{i+2} follows it into the columns.
+//   order on the tensor pipe:  dV_i | dQ^T_i  dK_i  dP^T_{i+1} | S^T_{i+2}
 //
 // Every wait is bounded (sm100_ptx.cuh).
 #include <atomic>
@@ -386,6 +387,9 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         zero_tail_rows(smem + L::kResB, it.sq.sk - it.n0, L::kHalves, lane);
       }
       if (G > 0 && !wait(L::bSRead, (G - 1) & 1u, 0x1201)) break;
+      if constexpr (FUSED) {      // the previous item's last dQ^T partial has left the S columns
+        if (G > 0 && !wait(L::bDqRead, (G - 1) & 1u, 0x1203)) break;
+      }
       if (!wait(L::bRingFull + (G & 1u), (G >> 1) & 1u, 0x1202)) break;
       if (lane == 0) AB200_STAMP(G, 15);
       // Last, partial query block of the sequence: rows of Q and dO beyond its end must not reach
@@ -400,16 +404,47 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       zero_ring_tail(G, 0);
       tc_fence_after();
       issue_s(G);
-      if constexpr (FUSED) {      // the previous iteration's dQ^T partial has left the dP columns
-        if (G > 0 && !wait(L::bDqRead, (G - 1) & 1u, 0x1203)) break;
-        tc_fence_after();
-      }
       issue_dp(G, !FUSED && it.niter == 1);
       if (lane == 0) AB200_STAMP(G, 8);
+      // dQ^T_g = K^T dS^T_g into the S columns (free once the compute warps have copied the next S^T
+      // out): both operands in shared memory, keys contracted in 8 steps of 16
+      auto issue_dqt = [&](uint32_t g) {
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+#if !defined(AB200_FUSED_KMAJOR_TEST)
+            mma_ss(tmem_base + kColS, k_mn + mnmajor_step(kk), ds_mn + mnmajor_step(kk), kIdescDQT, kk > 0 ? 1u : 0u);
+#elif AB200_FUSED_KMAJOR_TEST == 1   // timing experiments only (wrong results): both operands K-major
+            mma_ss(tmem_base + kColS, k_km + kmajor_step(kk), ds_km + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
+#elif AB200_FUSED_KMAJOR_TEST == 2   // A K-major, B N-major
+            mma_ss(tmem_base + kColS, k_km + kmajor_step(kk), ds_mn + mnmajor_step(kk),
+                   instr_desc_f16(Fmt<T>::code, 128, 128, 0, 1), kk > 0 ? 1u : 0u);
+#else                                // A M-major, B K-major
+            mma_ss(tmem_base + kColS, k_mn + mnmajor_step(kk), ds_km + kmajor_step(kk),
+                   instr_desc_f16(Fmt<T>::code, 128, 128, 1, 0), kk > 0 ? 1u : 0u);
+#endif
+          mma_commit(&bars[L::bDqFull]);
+        }
+        __syncwarp();
+      };
       for (int i = 0, mb_next = 1; i < it.niter; ++i, ++G, ++mb_next) {     // mb_next: (i + 1) % nmb
         const uint32_t s = G & 1u, par = G & 1u;
         if (mb_next == it.nmb) mb_next = 0;
-        if (!FUSED && i + 1 < it.niter) {
+        if constexpr (FUSED) {
+          // The S columns hold dQ^T_{g-1} (issued at the end of the previous iteration, when S_g had
+          // been copied out); S_{g+1} follows once the compute warps have fetched that partial.
+          if (i > 0) {
+            if (!wait(L::bDqRead, (G - 1) & 1u, 0x1580)) { ok = false; break; }
+            if (lane == 0) AB200_STAMP(G, 14);
+          } else if (!wait(L::bSRead, par, 0x1300)) { ok = false; break; }
+          if (i + 1 < it.niter) {
+            if (!wait(L::bRingFull + ((G + 1) & 1u), ((G + 1) >> 1) & 1u, 0x1400)) { ok = false; break; }
+            zero_ring_tail(G + 1, mb_next);
+            tc_fence_after();
+            issue_s(G + 1);
+            if (lane == 0) AB200_STAMP(G, 13);
+          }
+        } else if (i + 1 < it.niter) {
           // S_g sits in registers of every compute thread: its buffer can take S_{g+1} already.
           if (!wait(L::bSRead, par, 0x1300)) { ok = false; break; }
           if (!wait(L::bRingFull + ((G + 1) & 1u), ((G + 1) >> 1) & 1u, 0x1400)) { ok = false; break; }
@@ -433,54 +468,32 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         if (lane == 0) AB200_STAMP(G, 5);
         tc_fence_after();
         if constexpr (FUSED) {
-          if (elect_one()) {
-            // dQ^T_g = K^T dS^T_g into the dP columns (dV, issued above, has consumed P^T there);
-            // both operands in shared memory, keys contracted in 8 steps of 16
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              mma_ss(tmem_base + kColDP, k_mn + mnmajor_step(kk), ds_mn + mnmajor_step(kk), kIdescDQT, kk > 0 ? 1u : 0u);
-            mma_commit(&bars[L::bDqFull]);
-          }
-          __syncwarp();
+          // dQ^T_g goes first: the compute warps, now in iteration g+1, need it after their first
+          // exponentials; it takes the S columns as soon as they have copied S_{g+1} out.
           if (i + 1 < it.niter) {
-            // S^T_{g+1} goes between dQ^T_g and dK_g: the adders then have two GEMMs' time to take the
-            // partial out of tensor memory before dP^T_{g+1} needs its columns.
-            if (!wait(L::bSRead, par, 0x1300)) { ok = false; break; }
-            if (!wait(L::bRingFull + ((G + 1) & 1u), ((G + 1) >> 1) & 1u, 0x1400)) { ok = false; break; }
-            zero_ring_tail(G + 1, mb_next);
+            if (!wait(L::bSRead, (G + 1) & 1u, 0x1301)) { ok = false; break; }
             tc_fence_after();
-            issue_s(G + 1);
+            issue_dqt(G);
+            if (lane == 0) AB200_STAMP(G, 9);
           }
-          if (elect_one()) {
-            // dK += dS^T Q_g  (dS^T from shared memory, K-major)
-            const uint64_t qa = q_mn + (uint64_t)(s * kStageStep);
+        }
+        if (elect_one()) {   // dK += dS^T Q_g  (dS^T: the next 16 packed columns)
+          const uint64_t qa = q_mn + (uint64_t)(s * kStageStep);
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              mma_ss(tmem_base + kColAcc1, ds_km + kmajor_step(kk), qa + mnmajor_step(kk), kIdescDK, kk > 0 ? 1u : first);
-            mma_commit(&bars[L::bRingEmpty + s]);
-            if (i + 1 == it.niter) {
-              mma_commit(&bars[L::bAccDone]);
-              mma_commit(&bars[L::bResEmpty]);     // K was still being read by dQ^T
-            }
-          }
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + 16u + split_a_col(kk), qa + mnmajor_step(kk), kIdescDK,
+                   kk > 0 ? 1u : first);
+          mma_commit(&bars[L::bRingEmpty + s]);
+          if (i + 1 == it.niter) mma_commit(&bars[L::bAccDone]);
+        }
+        __syncwarp();
+        if (i + 1 < it.niter) {
+          issue_dp(G + 1, !FUSED && i + 2 == it.niter);
+        } else if constexpr (FUSED) {
+          // the item's last partial: the S columns are free (no S^T of this item follows)
+          issue_dqt(G);
+          if (elect_one()) mma_commit(&bars[L::bResEmpty]);      // K was still being read by dQ^T
           __syncwarp();
-          if (i + 1 < it.niter) {
-            if (!wait(L::bDqRead, par, 0x1580)) { ok = false; break; }
-            tc_fence_after();
-            issue_dp(G + 1, false);
-          }
-        } else {
-          if (elect_one()) {   // dK += dS^T Q_g  (dS^T: the next 16 packed columns)
-            const uint64_t qa = q_mn + (uint64_t)(s * kStageStep);
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              mma_ts(tmem_base + kColAcc1, tmem_base + kColDP + 16u + split_a_col(kk), qa + mnmajor_step(kk), kIdescDK,
-                     kk > 0 ? 1u : first);
-            mma_commit(&bars[L::bRingEmpty + s]);
-            if (i + 1 == it.niter) mma_commit(&bars[L::bAccDone]);
-          }
-          __syncwarp();
-          if (i + 1 < it.niter) issue_dp(G + 1, i + 2 == it.niter);
         }
       }
       if (!ok) break;
@@ -574,6 +587,26 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       if (n >= sq.sk) { col_lo = 1; col_hi = 0; }
       // the tightest bounds over the warp's rows: a block needs masking iff it is not inside them
       const int warp_lo = __reduce_max_sync(0xffffffffu, col_lo), warp_hi = __reduce_min_sync(0xffffffffu, col_hi);
+      // Fused form: the dQ^T partial of iteration g (head dim x queries, in the S columns) is taken
+      // out during iteration g+1.  This thread owns head-dim row d = its TMEM lane and the 32 query
+      // columns of its warpgroup; for a fixed query the warp's lanes add to 32 consecutive floats
+      // of the accumulator row (one 128-byte red.global.add).  dq_dst / dq_rows describe the
+      // partial that is pending.
+      float* dq_dst = nullptr;
+      int dq_rows = 0;
+      auto dq_add8 = [&](const float* v, int c8) {
+        if (r < p.dqk) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int c = 8 * c8 + j;
+#ifndef AB200_FUSED_NO_RED
+            if (c < dq_rows) atomicAdd(dq_dst + (int64_t)c * p.dqk, v[j]);
+#else
+            if (c < dq_rows && v[j] == 123456.f) dq_dst[(int64_t)c * p.dqk] = 0.f;
+#endif
+          }
+        }
+      };
       for (int i = 0, hg = 0, mb = 0; i < it.niter; ++i, ++G) {     // hg, mb: i / nmb, i % nmb
         const int s = (int)(G & 1u);
         const uint32_t par = G & 1u;
@@ -600,19 +633,60 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         // Common case: one packed FMA per two elements.  With bias, or when the logsumexp is so
         // large that product rounding matters (the aux warp flags that), scale first and subtract
         // second, so that the forward's reference point cancels exactly.
+        // Fused form: the previous iteration's dQ^T partial was issued when this warp released the S
+        // columns just now and completes under the first exponentials; it is then fetched eight
+        // query columns at a time and added out between the remaining ones (the exponentials keep
+        // the special-function unit busy and leave the load/store unit idle).
+        const bool dq_now = FUSED && i > 0;
+        auto exp4 = [&](int c4, float2 sc2) {
+          const float4 l4 = lds128(lse2 + 16u * c4);
+          const float2 a = fma2(make_float2(pr[4 * c4], pr[4 * c4 + 1]), sc2, make_float2(l4.x, l4.y));
+          const float2 b = fma2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]), sc2, make_float2(l4.z, l4.w));
+          pr[4 * c4 + 0] = ex2(a.x);
+          pr[4 * c4 + 1] = ex2(a.y);
+          pr[4 * c4 + 2] = ex2(b.x);
+          pr[4 * c4 + 3] = ex2(b.y);
+        };
         if (!p.has_bias && aux_flag[s] == 0) {
           const float2 sc2 = make_float2(p.qk_scale, p.qk_scale);
+          if (dq_now) {
 #pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4) {
-            const float4 l4 = lds128(lse2 + 16u * c4);
-            const float2 a = fma2(make_float2(pr[4 * c4], pr[4 * c4 + 1]), sc2, make_float2(l4.x, l4.y));
-            const float2 b = fma2(make_float2(pr[4 * c4 + 2], pr[4 * c4 + 3]), sc2, make_float2(l4.z, l4.w));
-            pr[4 * c4 + 0] = ex2(a.x);
-            pr[4 * c4 + 1] = ex2(a.y);
-            pr[4 * c4 + 2] = ex2(b.x);
-            pr[4 * c4 + 3] = ex2(b.y);
+            for (int c4 = 0; c4 < 4; ++c4) exp4(c4, sc2);
+            if (!mbar_wait(&bars[L::bDqFull], (G - 1) & 1u, abort_flag, status, 0x1D00)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c8 = 0; c8 < 4; ++c8) {
+              float dqv[8];
+              tmem_ld8f(tmem_base + lane_addr + kColS + cbase + 8 * c8, dqv);
+              exp4(4 + c8, sc2);
+              tmem_wait_ld();
+              if (c8 == 3) {      // everything fetched: the S columns can take the next S^T
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars[L::bDqRead]);
+              }
+              dq_add8(dqv, c8);
+            }
+            __syncwarp();
+          } else {
+#pragma unroll
+            for (int c4 = 0; c4 < 8; ++c4) exp4(c4, sc2);
           }
         } else {
+          if (dq_now) {
+            if (!mbar_wait(&bars[L::bDqFull], (G - 1) & 1u, abort_flag, status, 0x1D00)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c8 = 0; c8 < 4; ++c8) {
+              float dqv[8];
+              tmem_ld8f(tmem_base + lane_addr + kColS + cbase + 8 * c8, dqv);
+              tmem_wait_ld();
+              dq_add8(dqv, c8);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[L::bDqRead]);
+          }
 #pragma unroll
           for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
           if (p.has_bias && n < sq.sk) {
@@ -700,6 +774,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
             pk[2 * c4] = pack2<T>(a.x, a.y);
             pk[2 * c4 + 1] = pack2<T>(b.x, b.y);
           }
+          tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16, pk);
           if constexpr (FUSED) {
             if (i == 0 && live > 0 &&
                 !mbar_wait(&bars[L::bStageFree], (live - 1) & 1u, abort_flag, status, 0x1E00)) { ok = false; break; }
@@ -712,12 +787,10 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
               *reinterpret_cast<uint4*>(row + (((((wg & 1) << 2) + j) ^ (r & 7)) << 4)) =
                   make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
             fence_proxy_async_smem();
-          } else {
-            tmem_st16(tmem_base + lane_addr + kColDP + cbase + 16, pk);
           }
         }
         if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 11);
-        if constexpr (!FUSED) tmem_wait_st();
+        tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
@@ -725,33 +798,9 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           mbar_arrive(&bars[L::bAuxEmpty + s]);
         }
         if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 3);
-        if constexpr (FUSED) {
-          // dQ^T_g (head dim x queries) arrives in the dP columns two GEMMs later, while this warp
-          // would only wait for S^T_{g+1}.  This thread takes head-dim row d = its TMEM lane and the
-          // 32 query columns of its warpgroup; for a fixed query the warp's lanes add to 32
-          // consecutive floats of the accumulator row.
-          if (!mbar_wait(&bars[L::bDqFull], par, abort_flag, status, 0x1D00)) { ok = false; break; }
-          tc_fence_after();
-          float dqv[32];
-          tmem_ld32f(tmem_base + lane_addr + kColDP + cbase, dqv);
-          tmem_wait_ld();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars[L::bDqRead]);      // the dP columns can take dP^T_{g+1}
-          // (mbase is the first query row of this thread's columns)
-          float* acc = dq_acc + (((int64_t)sq.bidx * p.hq + h) * p.dq.n[2] + sq.q0 + mbase) * p.dqk + r;
-          const int rows = sq.sq - mbase;
-          if (r < p.dqk) {
-#pragma unroll
-            for (int c = 0; c < 32; ++c)
-#ifndef AB200_FUSED_NO_RED
-              if (c < rows) atomicAdd(acc + (int64_t)c * p.dqk, dqv[c]);
-#else
-              if (c < rows && dqv[c] == 123456.f) acc[(int64_t)c * p.dqk] = 0.f;
-#endif
-          }
-          __syncwarp();
-          if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 12);
+        if constexpr (FUSED) {      // this iteration's dQ^T partial is taken out during the next one
+          dq_dst = dq_acc + (((int64_t)sq.bidx * p.hq + h) * p.dq.n[2] + sq.q0 + mbase) * p.dqk + r;
+          dq_rows = sq.sq - mbase;
         }
       }
       if (!ok) break;
@@ -759,6 +808,22 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       if (!mbar_wait(&bars[L::bAccDone], live & 1u, abort_flag, status, 0x1A00)) { ok = false; break; }
       if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G - 1, 13);
       ++live;
+      if constexpr (FUSED) {
+        // The item's last partial (it also is the last reader of the dS^T tile, which the write-out
+        // below reuses as its staging tile).
+        if (!mbar_wait(&bars[L::bDqFull], (G - 1) & 1u, abort_flag, status, 0x1D01)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          float dqv[8];
+          tmem_ld8f(tmem_base + lane_addr + kColS + cbase + 8 * c8, dqv);
+          tmem_wait_ld();
+          dq_add8(dqv, c8);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[L::bDqRead]);
+      }
       if (wg < HD / 32) {
         // Each warp transposes its 32 rows x 32 columns through the staging tile, so that the global
         // stores are 64-byte row segments instead of 16 bytes per row.

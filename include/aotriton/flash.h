@@ -43,9 +43,10 @@ using LT4 = AOTRITON_NS::LazyTensor<4>;
 
 // Per-call knobs.  force_backend_index: -1 automatic, 0 the general kernels,
 // 1 the tcgen05 kernels (hipErrorNotSupported if the shape is outside their
-// range).  deterministic: true keeps the two-kernel backward, whose sums have a fixed
-// order; false (the default) lets attn_bwd use DQ_ACC and the fused backward, which
-// adds dQ partials with floating-point atomics (run-to-run differences in the last bits).
+// range), 2 automatic, with the fused backward where it applies: it uses DQ_ACC
+// and adds dQ partials with floating-point atomics (run-to-run differences in
+// the last bits).  deterministic: true never uses the fused backward; the automatic
+// choice does not either, since the two-kernel backward measured faster.
 struct AOTRITON_API attn_options {
   int force_backend_index = -1;
   bool deterministic = false;

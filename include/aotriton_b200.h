@@ -115,8 +115,9 @@ typedef struct ab200_attn_bwd_args {
   int32_t deterministic;            /* attn_options::deterministic: non-zero forbids the fused form below */
   /* Optional fp32 dQ accumulator (the "DQ_ACC" lazy tensor, include/aotriton/flash.h:170): contiguous
    * in dq's logical order, dq.size[0] * dq.size[1] * dq.size[2] * head_dim_qk floats, ZERO on entry
-   * (the reference's allocator callback returns zeros).  When it is given, `deterministic` is 0 and
-   * the problem qualifies (ab200_bwd_uses_dq_acc), ab200_attn_bwd runs the fused form: one kernel
+   * (the reference's allocator callback returns zeros).  When it is given, `deterministic` is 0, the
+   * fused form was asked for (kernel family 3) and the problem qualifies (ab200_bwd_uses_dq_acc),
+   * ab200_attn_bwd runs the fused form: one kernel
    * produces dK, dV and adds dQ partials here with atomics, a conversion kernel writes dq.  The
    * accumulator holds the unscaled sum afterwards.  NULL selects the two-kernel form. */
   float* dq_acc;
@@ -158,8 +159,8 @@ AB200_API int ab200_attn_bwd(const ab200_attn_bwd_args* args, void* stream);
 #define AB200_STATIC_DELTA_FLOATS (1u << 20)
 AB200_API int ab200_attn_bwd_static_scratch(const ab200_attn_bwd_args* args, void* stream);
 
-/* 1 when ab200_attn_bwd would use args->dq_acc if it were given (tcgen05 kernels apply, head dim
- * above 64, no dBias requested, deterministic == 0), else 0; lets a caller acquire the accumulator
+/* 1 when ab200_attn_bwd would use args->dq_acc if it were given (kernel family 3 selected, tcgen05
+ * kernels apply, head dim above 64, no dBias requested, deterministic == 0), else 0; lets a caller acquire the accumulator
  * only when it is needed, as attn_bwd does with the reference's lazy tensor
  * (modules/flash/csrc/attn_bwd.cc:140-158). */
 AB200_API int ab200_bwd_uses_dq_acc(const ab200_attn_bwd_args* args, void* stream);
@@ -195,8 +196,10 @@ AB200_API int ab200_multiprocessor_count(void* stream);
 
 /* Selects the kernel family: 0 = automatic (tcgen05 kernels where they apply),
  * 1 = force the general SIMT kernels, 2 = require tcgen05 kernels (unsupported
- * shapes then return hipErrorNotSupported).  Counterpart of
- * attn_options::force_backend_index (include/aotriton/flash.h:38-40).  Returns the old value. */
+ * shapes then return hipErrorNotSupported), 3 = like 0, and the backward takes its
+ * fused form whenever a dQ accumulator is supplied and the problem qualifies.
+ * Counterpart of attn_options::force_backend_index (include/aotriton/flash.h:38-40).
+ * Per calling thread.  Returns the old value. */
 AB200_API int ab200_set_kernel_family(int family);
 
 /* Which family the most recent forward / backward launch of this thread used

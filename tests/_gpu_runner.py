@@ -5,9 +5,9 @@ import torch
 
 from aotriton_b200 import cabi
 
-# "fused": automatic choice with a dQ accumulator supplied, so that the backward may take the fused
+# "fused": automatic choice with the fused backward requested and a dQ accumulator supplied, so that the backward takes the fused
 # (atomic-dQ) form where it applies
-FAMILY = {"auto": 0, "general": 1, "sm100": 2, "fused": 0}
+FAMILY = {"auto": 0, "general": 1, "sm100": 2, "fused": 3}
 
 
 def dev(t):

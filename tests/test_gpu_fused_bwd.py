@@ -21,7 +21,11 @@ def _bwd(q, k, v, out, do, lse, *, fused, deterministic=False, **prob):
     dq, dk, dv = (torch.full_like(t, float("nan")) for t in (q, k, v))
     delta = torch.empty_like(lse)
     acc = torch.zeros(tuple(q.shape), dtype=torch.float32, device="cuda") if fused else None
-    err = cabi.attn_bwd(q, k, v, out, do, dq, dk, dv, lse, delta, dq_acc=acc, deterministic=deterministic, **prob)
+    old = cabi.lib().ab200_set_kernel_family(3 if fused else 2)      # 3: fused backward where it applies
+    try:
+        err = cabi.attn_bwd(q, k, v, out, do, dq, dk, dv, lse, delta, dq_acc=acc, deterministic=deterministic, **prob)
+    finally:
+        cabi.lib().ab200_set_kernel_family(old)
     assert err == 0, err
     torch.cuda.synchronize()
     return dq, dk, dv, cabi.lib().ab200_last_bwd_family()
@@ -136,6 +140,7 @@ def test_fused_backward_through_the_operator_api():
         dq, dk, dv = (torch.full_like(t, float("nan")) for t in (q, k, v))
         opts = flash.attn_options()
         opts.deterministic = deterministic
+        opts.force_backend_index = 2          # fused backward where it applies
         like = flash.T4(dq.data_ptr(), tuple(dq.size()), tuple(dq.stride()), flash.cast_dtype(dq.dtype))
 
         def factory():
