@@ -229,7 +229,11 @@ __device__ __forceinline__ DkdvItem dkdv_item(const Params& p, int w) {
   return it;
 }
 
-template <typename T, int HD, bool FUSED>
+// EXACT: a dense problem whose sequence lengths are multiples of 128 and whose head dimensions equal
+// HD: every tile is full, so the instantiation carries no tail handling and fixed GEMM shapes (the
+// MMA issuer's loop is latency-critical: even untaken branches and call sites in it cost several
+// per cent of the kernel's time).
+template <typename T, int HD, bool FUSED, bool EXACT>
 __global__ void __launch_bounds__(FUSED ? kFusedThreads : kBwdThreads, 1)
 sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -332,9 +336,10 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     // Contractions over a head dimension run over it rounded up to 16, products into a head
     // dimension produce it rounded up to 16 (the copies zero-fill up to the 64-column box).
     constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
-    const uint32_t kIdescDV = instr_desc_f16(Fmt<T>::code, 128, (uint32_t)((p.dvo + 15) & ~15), 0, 1);
-    const uint32_t kIdescDK = instr_desc_f16(Fmt<T>::code, 128, (uint32_t)((p.dqk + 15) & ~15), 0, 1);
-    const int ksteps_qk = (p.dqk + 15) >> 4, ksteps_vo = (p.dvo + 15) >> 4;
+    // (EXACT: all equal the kernel's head dimension, known at compile time)
+    const uint32_t kIdescDV = instr_desc_f16(Fmt<T>::code, 128, EXACT ? (uint32_t)HD : (uint32_t)((p.dvo + 15) & ~15), 0, 1);
+    const uint32_t kIdescDK = instr_desc_f16(Fmt<T>::code, 128, EXACT ? (uint32_t)HD : (uint32_t)((p.dqk + 15) & ~15), 0, 1);
+    const int ksteps_qk = EXACT ? HD / 16 : (p.dqk + 15) >> 4, ksteps_vo = EXACT ? HD / 16 : (p.dvo + 15) >> 4;
     constexpr uint32_t kStageStep = L::kTile >> 4;
     const uint64_t k_km = kmajor_base(smem_u32(smem + L::kResA)), v_km = kmajor_base(smem_u32(smem + L::kResB));
     const uint64_t q_km = kmajor_base(smem_u32(smem + L::kRingA)), do_km = kmajor_base(smem_u32(smem + L::kRingB));
@@ -382,9 +387,11 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       // Last, partial key block of the sequence: keys beyond its end are rows of S^T / dP^T that are
       // never stored, but in the fused form they are contracted over by dQ^T, where a zero dS^T times
       // a non-finite K row (or dS^T made non-finite by a V row) would poison the sum.
-      if (it.sq.sk - it.n0 < kBlk) {
-        zero_tail_rows(smem + L::kResA, it.sq.sk - it.n0, L::kHalves, lane);
-        zero_tail_rows(smem + L::kResB, it.sq.sk - it.n0, L::kHalves, lane);
+      if constexpr (!EXACT) {
+        if (it.sq.sk - it.n0 < kBlk) {
+          zero_tail_rows(smem + L::kResA, it.sq.sk - it.n0, L::kHalves, lane);
+          zero_tail_rows(smem + L::kResB, it.sq.sk - it.n0, L::kHalves, lane);
+        }
       }
       if (G > 0 && !wait(L::bSRead, (G - 1) & 1u, 0x1201)) break;
       if constexpr (FUSED) {      // the previous item's last dQ^T partial has left the S columns
@@ -395,10 +402,12 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       // Last, partial query block of the sequence: rows of Q and dO beyond its end must not reach
       // the dV / dK products (a zero probability times a non-finite value would poison them).
       auto zero_ring_tail = [&](uint32_t g, int mb) {
-        const int valid = it.sq.sq - (it.mb_lo + mb) * kBlk;
-        if (valid < kBlk) {
-          zero_tail_rows(smem + L::kRingA + (g & 1u) * L::kTile, valid, L::kHalves, lane);
-          zero_tail_rows(smem + L::kRingB + (g & 1u) * L::kTile, valid, L::kHalves, lane);
+        if constexpr (!EXACT) {
+          const int valid = it.sq.sq - (it.mb_lo + mb) * kBlk;
+          if (valid < kBlk) {
+            zero_tail_rows(smem + L::kRingA + (g & 1u) * L::kTile, valid, L::kHalves, lane);
+            zero_tail_rows(smem + L::kRingB + (g & 1u) * L::kTile, valid, L::kHalves, lane);
+          }
         }
       };
       zero_ring_tail(G, 0);
@@ -889,7 +898,7 @@ struct DqSmem {
 
 // =========================================================================================
 // dQ (+ dBias).  grid = (cdiv(max_sq, 128), Hq, batch)
-template <typename T, int HD>
+template <typename T, int HD, bool EXACT>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CUtensorMap tm_q,
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -994,8 +1003,8 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     // flow warp-uniform lets the descriptors live in uniform registers, which makes the issue of
     // a GEMM several times cheaper in issue slots than a single-lane branch.
     constexpr uint32_t kIdescSS = instr_desc_f16(Fmt<T>::code, 128, 128, 0, 0);
-    const uint32_t kIdescDQ = instr_desc_f16(Fmt<T>::code, 128, (uint32_t)((p.dqk + 15) & ~15), 0, 1);
-    const int ksteps_qk = (p.dqk + 15) >> 4, ksteps_vo = (p.dvo + 15) >> 4;
+    const uint32_t kIdescDQ = instr_desc_f16(Fmt<T>::code, 128, EXACT ? (uint32_t)HD : (uint32_t)((p.dqk + 15) & ~15), 0, 1);
+    const int ksteps_qk = EXACT ? HD / 16 : (p.dqk + 15) >> 4, ksteps_vo = EXACT ? HD / 16 : (p.dvo + 15) >> 4;
     constexpr uint32_t kStageStep = L::kTile >> 4;
     const uint64_t q_km = kmajor_base(smem_u32(smem + L::kResA)), do_km = kmajor_base(smem_u32(smem + L::kResB));
     const uint64_t k_km = kmajor_base(smem_u32(smem + L::kK)), v_km = kmajor_base(smem_u32(smem + L::kV));
@@ -1006,12 +1015,14 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     // Last, partial key block of the sequence: rows of K and V beyond its end must not reach the
     // dP and dQ products (a zero dS times a non-finite K row, or dO times a non-finite V row).
     auto zero_tail = [&](int base, int i, int stage) {
-      const int valid = sq.sk - (jb_lo + i) * kBlk;
-      if (valid < kBlk) zero_tail_rows(smem + base + stage * L::kTile, valid, L::kHalves, lane);
+      if constexpr (!EXACT) {
+        const int valid = sq.sk - (jb_lo + i) * kBlk;
+        if (valid < kBlk) zero_tail_rows(smem + base + stage * L::kTile, valid, L::kHalves, lane);
+      }
     };
     auto issue_s = [&](int i) {      // S = Q K_i^T
       zero_tail(L::kK, i, i % L::kKStages);
-      tc_fence_after();
+      if constexpr (!EXACT) tc_fence_after();
       const uint64_t ka = k_km + (uint64_t)((uint32_t)(i % L::kKStages) * kStageStep);
       if (elect_one()) {
 #pragma unroll
@@ -1024,7 +1035,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     };
     auto issue_dp = [&](int i) {     // dP = dO V_i^T, into dP buffer i & 1; frees V's ring stage
       zero_tail(L::kV, i, i & 1);
-      tc_fence_after();
+      if constexpr (!EXACT) tc_fence_after();
       const uint64_t va = v_km + (uint64_t)((uint32_t)(i & 1) * kStageStep);
       const uint32_t d = tmem_base + kColDP + (uint32_t)(i & 1) * 128u;
       if (elect_one()) {
@@ -1283,7 +1294,8 @@ cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st, float* dq_
   // make the stream's device, and remembered.
   struct PerDevice { std::atomic<unsigned int*> status{nullptr}, tickets{nullptr}; std::atomic<int> sms{0}; };
   static PerDevice per_device[64];
-  static std::atomic<bool> attr_set[64][3];
+  static std::atomic<bool> attr_set[64][5];
+  const bool exact = p.varlen_mode == 0 && p.max_sq % 128 == 0 && p.max_sk % 128 == 0 && p.dqk == HD && p.dvo == HD;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
@@ -1303,10 +1315,10 @@ cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st, float* dq_
   if (which == 1 || which == 3) {
     const bool fused = which == 3;
     if (fused && HD != 128) return cudaErrorInvalidValue;
-    auto kern_split = sm100_bwd_dkdv_kernel<T, HD, false>;
-    auto kern_fused = sm100_bwd_dkdv_kernel<T, 128, true>;
+    auto kern_split = exact ? sm100_bwd_dkdv_kernel<T, HD, false, true> : sm100_bwd_dkdv_kernel<T, HD, false, false>;
+    auto kern_fused = sm100_bwd_dkdv_kernel<T, 128, true, false>;
     e = fused ? set_smem(2, reinterpret_cast<const void*>(kern_fused), BwdSmem<128>::kDynamic)
-              : set_smem(0, reinterpret_cast<const void*>(kern_split), L::kDynamic);
+              : set_smem(exact ? 3 : 0, reinterpret_cast<const void*>(kern_split), L::kDynamic);
     if (e != cudaSuccess) return e;
     const int nitems = ((p.max_sk + kBlk - 1) / kBlk) * ((p.hk * p.batch + 7) / 8) * 8;
     int sms = pd.sms.load(std::memory_order_acquire);
@@ -1329,10 +1341,11 @@ cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st, float* dq_
     else
       kern_split<<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status, nitems, ticket, nullptr);
   } else {
-    e = set_smem(1, reinterpret_cast<const void*>(sm100_bwd_dq_kernel<T, HD>), DqSmem<HD>::kDynamic);
+    auto kern_dq = exact ? sm100_bwd_dq_kernel<T, HD, true> : sm100_bwd_dq_kernel<T, HD, false>;
+    e = set_smem(exact ? 4 : 1, reinterpret_cast<const void*>(kern_dq), DqSmem<HD>::kDynamic);
     if (e != cudaSuccess) return e;
     dim3 grid((p.max_sq + kBlk - 1) / kBlk, p.hq, p.batch);
-    sm100_bwd_dq_kernel<T, HD><<<grid, kBwdThreads, DqSmem<HD>::kDynamic, st>>>(p, tq, tk, tv, tdo, status);
+    kern_dq<<<grid, kBwdThreads, DqSmem<HD>::kDynamic, st>>>(p, tq, tk, tv, tdo, status);
   }
   count_launch();
   return cudaGetLastError();

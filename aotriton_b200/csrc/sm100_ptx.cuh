@@ -211,7 +211,9 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 // sequence, so the rows beyond the sequence's end hold a neighbour's tokens or padding, and a zero
 // probability times a non-finite value there would poison the product (the reference zero-fills
 // such rows with masked loads, modules/flash/kernel/masked_load_store.py:214-307).
-__device__ __forceinline__ void zero_tail_rows(uint8_t* tile, int valid_rows, int halves, int lane) {
+// (Not inlined on purpose: it runs at most once per sequence end, and its loops inside the MMA
+// issuer's loop cost that warp registers and instruction-cache room on every block.)
+static __device__ __noinline__ void zero_tail_rows(uint8_t* tile, int valid_rows, int halves, int lane) {
   const uint4 z = make_uint4(0u, 0u, 0u, 0u);
   for (int hf = 0; hf < halves; ++hf)
     for (int o = valid_rows * 128 + lane * 16; o < 16384; o += 512)
