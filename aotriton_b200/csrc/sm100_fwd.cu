@@ -127,7 +127,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
   // start together and the grid ends on light ones, while the CTAs in flight share the K/V of one
   // group of heads, which stays resident in L2.
 #ifndef AB200_FWD_HEAD_GROUP
-#define AB200_FWD_HEAD_GROUP 16
+#define AB200_FWD_HEAD_GROUP 32
 #endif
   int z = blockIdx.z, h = blockIdx.y, m0 = (int)(gridDim.x - 1 - blockIdx.x) * kCtaRows;
   if constexpr (AB200_FWD_HEAD_GROUP > 0) {
