@@ -16,15 +16,16 @@ CAUSAL_NONE, CAUSAL_WINDOWED = 0, 3
 WINDOW_TOP_LEFT, WINDOW_BOTTOM_RIGHT = -2147483647, -2147483646
 VARLEN_NONE, VARLEN_COMPACT, VARLEN_PADDED, VARLEN_STRIDED = 0, 1, 2, 3
 STATIC_DELTA_FLOATS = 1 << 20   # AB200_STATIC_DELTA_FLOATS
+SELECT_ALIGNED, SELECT_DBIAS, SELECT_FUSED_REQUESTED, SELECT_FORCE_GENERAL, SELECT_FORCE_TCGEN05 = 1, 2, 4, 8, 16
 
 # Exported symbols, in header order (checked by the CPU test-suite).
 SYMBOLS = [
-    "ab200_attn_fwd", "ab200_attn_bwd", "ab200_attn_bwd_static_scratch", "ab200_bwd_uses_dq_acc", "ab200_bwd_fused",
-    "ab200_bwd_postprocess", "ab200_bwd_preprocess", "ab200_bwd_dkdv", "ab200_bwd_dq",
+    "ab200_attn_fwd", "ab200_attn_bwd", "ab200_attn_bwd_static_scratch", "ab200_bwd_uses_dq_acc",
+    "ab200_bwd_fused", "ab200_bwd_postprocess", "ab200_bwd_preprocess", "ab200_bwd_dkdv", "ab200_bwd_dq",
     "ab200_debug_simulate_encoded_softmax", "ab200_check_gpu", "ab200_multiprocessor_count",
-    "ab200_set_kernel_family", "ab200_last_fwd_family", "ab200_last_bwd_family", "ab200_kernel_status",
-    "ab200_stream_check", "ab200_debug_bounded_wait_test", "ab200_launch_count",
-    "ab200_version",
+    "ab200_set_kernel_family", "ab200_select_variant", "ab200_last_fwd_family", "ab200_last_bwd_family",
+    "ab200_kernel_status", "ab200_stream_check", "ab200_debug_bounded_wait_test", "ab200_debug_host_calls",
+    "ab200_debug_host_call_count", "ab200_launch_count", "ab200_version",
 ]
 
 
@@ -82,12 +83,17 @@ def lib() -> C.CDLL:
             C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]
         L.ab200_check_gpu.argtypes = [C.c_void_p]
         L.ab200_multiprocessor_count.argtypes = [C.c_void_p]
+        L.ab200_select_variant.argtypes = [C.c_int] * 5
         L.ab200_set_kernel_family.argtypes = [C.c_int]
         L.ab200_kernel_status.argtypes = [C.c_int]
         L.ab200_kernel_status.restype = C.c_uint
         L.ab200_stream_check.argtypes = [C.c_void_p]
         L.ab200_debug_bounded_wait_test.argtypes = [C.c_int, C.c_uint]
         L.ab200_debug_bounded_wait_test.restype = None
+        L.ab200_debug_host_calls.argtypes = [C.c_int] * 4
+        L.ab200_debug_host_calls.restype = None
+        L.ab200_debug_host_call_count.argtypes = [C.c_int]
+        L.ab200_debug_host_call_count.restype = C.c_uint64
         L.ab200_launch_count.restype = C.c_uint64
         L.ab200_version.restype = C.c_char_p
         _lib = L

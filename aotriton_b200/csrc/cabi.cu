@@ -30,6 +30,122 @@ static std::atomic<uint64_t> g_failed_devices{0};
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+// ---- host-call table -------------------------------------------------------------------------
+namespace {
+std::atomic<int> g_fake_device{0};              // 1: pretend an sm_100 device, skip symbol look-ups and launches
+std::atomic<int> g_fail_call{-1}, g_fail_code{0}, g_fail_after{0};
+std::atomic<uint64_t> g_call_count[kNumHostCalls];
+
+// true when this call is the one a test asked to fail; counts the call either way
+bool injected(int id, cudaError_t* code) {
+  g_call_count[id].fetch_add(1, std::memory_order_relaxed);
+  if (g_fail_call.load(std::memory_order_relaxed) != id) return false;
+  if (g_fail_after.fetch_sub(1, std::memory_order_relaxed) != 0) return false;
+  *code = static_cast<cudaError_t>(g_fail_code.load(std::memory_order_relaxed));
+  return true;
+}
+bool fake() { return g_fake_device.load(std::memory_order_relaxed) != 0; }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn driver_encoder() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    (void)cudaGetLastError();
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+cudaError_t h_get_device(int* dev) {
+  cudaError_t c;
+  if (injected(kCallGetDevice, &c)) return c;
+  if (fake()) { *dev = 0; return cudaSuccess; }
+  return cudaGetDevice(dev);
+}
+cudaError_t h_set_device(int dev) {
+  cudaError_t c;
+  if (injected(kCallSetDevice, &c)) return c;
+  if (fake()) return cudaSuccess;
+  return cudaSetDevice(dev);
+}
+cudaError_t h_stream_device(cudaStream_t st, int* dev) {
+  cudaError_t c;
+  if (injected(kCallStreamDevice, &c)) return c;
+  if (fake()) { *dev = 0; return cudaSuccess; }
+#if CUDART_VERSION >= 12080
+  return cudaStreamGetDevice(st, dev);
+#else
+  (void)st;
+  return cudaGetDevice(dev);
+#endif
+}
+cudaError_t h_device_attr(int* value, cudaDeviceAttr attr, int dev) {
+  cudaError_t c;
+  if (injected(kCallDeviceAttr, &c)) return c;
+  if (fake()) {
+    *value = attr == cudaDevAttrComputeCapabilityMajor ? 10 : (attr == cudaDevAttrMultiProcessorCount ? 148 : 0);
+    return cudaSuccess;
+  }
+  return cudaDeviceGetAttribute(value, attr, dev);
+}
+cudaError_t h_func_set_smem(const void* fn, int bytes) {
+  cudaError_t c;
+  if (injected(kCallFuncSetSmem, &c)) return c;
+  if (fake()) return cudaSuccess;
+  return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+cudaError_t h_symbol_address(void** ptr, const void* symbol) {
+  cudaError_t c;
+  if (injected(kCallSymbolAddress, &c)) return c;
+  if (fake()) { *ptr = reinterpret_cast<void*>(uintptr_t(0x1000)); return cudaSuccess; }   // never dereferenced
+  return cudaGetSymbolAddress(ptr, symbol);
+}
+cudaError_t h_memset_async(void* ptr, int value, size_t bytes, cudaStream_t st) {
+  cudaError_t c;
+  if (injected(kCallMemsetAsync, &c)) return c;
+  if (fake()) return cudaSuccess;
+  return cudaMemsetAsync(ptr, value, bytes, st);
+}
+cudaError_t h_launch(const void* fn, dim3 grid, dim3 block, void** args, size_t smem, cudaStream_t st) {
+  cudaError_t c;
+  if (injected(kCallLaunch, &c)) return c;
+  if (fake()) return cudaSuccess;
+  return cudaLaunchKernel(fn, grid, block, args, smem, st);
+}
+int h_encode_tiled(CUtensorMap* map, CUtensorMapDataType type, cuuint32_t rank, void* base, const cuuint64_t* dims,
+                   const cuuint64_t* strides, const cuuint32_t* box, const cuuint32_t* estr, CUtensorMapInterleave il,
+                   CUtensorMapSwizzle sw, CUtensorMapL2promotion l2, CUtensorMapFloatOOBfill fill) {
+  cudaError_t c;
+  if (injected(kCallEncodeTiled, &c)) return (int)c;
+  if (fake()) { *map = CUtensorMap{}; return 0; }
+  EncodeTiledFn enc = driver_encoder();
+  if (!enc) return 100;     // CUDA_ERROR_NO_DEVICE: no driver to encode with
+  return (int)enc(map, type, rank, base, dims, strides, box, estr, il, sw, l2, fill);
+}
+cudaError_t h_stream_sync(cudaStream_t st) {
+  cudaError_t c;
+  if (injected(kCallStreamSync, &c)) return c;
+  if (fake()) return cudaSuccess;
+  return cudaStreamSynchronize(st);
+}
+bool h_have_encoder() { return fake() || driver_encoder() != nullptr; }
+}  // namespace
+
+bool host_pretends() { return fake(); }
+
+const HostCalls& host() {
+  static const HostCalls table = {h_get_device,  h_set_device,   h_stream_device, h_device_attr,
+                                  h_func_set_smem, h_symbol_address, h_memset_async, h_launch,
+                                  h_encode_tiled,  h_stream_sync,   h_have_encoder};
+  return table;
+}
+
 namespace {
 
 enum : int { kErrInvalidValue = 1, kErrNoBinaryForGpu = 209, kErrLaunchFailure = 719, kErrNotSupported = 801 };
@@ -45,11 +161,12 @@ DeviceInfo device_info(int dev) {
   std::lock_guard<std::mutex> lock(mu);
   if (!table[dev].known) {
     DeviceInfo d;
-    if (cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&d.minor, cudaDevAttrComputeCapabilityMinor, dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) {
+    if (host().device_attr(&d.major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess &&
+        host().device_attr(&d.minor, cudaDevAttrComputeCapabilityMinor, dev) == cudaSuccess &&
+        host().device_attr(&d.sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) {
       d.known = true;
-      table[dev] = d;
+      if (!fake()) table[dev] = d;       // (a pretended device is not remembered)
+      else return d;
     } else {
       (void)cudaGetLastError();
     }
@@ -59,11 +176,9 @@ DeviceInfo device_info(int dev) {
 
 int stream_device(cudaStream_t st) {
   int dev = -1;
-#if CUDART_VERSION >= 12080
-  if (st != nullptr && cudaStreamGetDevice(st, &dev) == cudaSuccess) return dev;
-  (void)cudaGetLastError();
-#endif
-  if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); return -1; }
+  if (st != nullptr && host().stream_device(st, &dev) == cudaSuccess) return dev;
+  if (!fake()) (void)cudaGetLastError();
+  if (host().get_device(&dev) != cudaSuccess) { if (!fake()) (void)cudaGetLastError(); return -1; }
   return dev;
 }
 
@@ -84,11 +199,11 @@ struct DeviceGuard {
   bool switched_ = false;
   explicit DeviceGuard(cudaStream_t st) {
     const int dev = stream_device(st);
-    if (dev >= 0 && cudaGetDevice(&old_) == cudaSuccess && old_ != dev)
-      switched_ = cudaSetDevice(dev) == cudaSuccess;
-    (void)cudaGetLastError();
+    if (dev >= 0 && host().get_device(&old_) == cudaSuccess && old_ != dev)
+      switched_ = host().set_device(dev) == cudaSuccess;
+    if (!fake()) (void)cudaGetLastError();
   }
-  ~DeviceGuard() { if (switched_) { (void)cudaSetDevice(old_); } }
+  ~DeviceGuard() { if (switched_) { (void)host().set_device(old_); } }
 };
 
 bool rows_16byte(const ab200_view4& v) {
@@ -137,7 +252,28 @@ int fill_common(const ab200_attn_problem& a, Params& p) {
   return 0;
 }
 
+// ---- static selection table ---------------------------------------------------------------
+// What the reference looks up in its tuning database (tables FLASH$op_attn_fwd / FLASH$op_attn_bwd,
+// keyed by dtype, head-dim bin, bias, dropout, causal and sequence-length bins) is a fixed table here:
+// the first row whose dtype set and head-dim bound cover the problem names the kernel variant and
+// the head-dim instantiation.  Alignment, the caller's forced family and the fused-backward request
+// are applied on top (ab200_select_variant).
+enum : int { kOpFwd = 0, kOpBwd = 1 };
+enum : int { kVarGeneral = 1, kVarTcgen05 = 2, kVarTcgen05Fused = 3 };
+struct SelectionRow { int op; unsigned dtype_mask; int dmax; int hd; int variant; };
+constexpr unsigned kHalfTypes = (1u << AB200_DTYPE_FP16) | (1u << AB200_DTYPE_BF16);
+constexpr unsigned kAllTypes = kHalfTypes | (1u << AB200_DTYPE_FP32);
+constexpr SelectionRow kSelection[] = {
+    {kOpFwd, kHalfTypes, 64, 64, kVarTcgen05},   {kOpFwd, kHalfTypes, 128, 128, kVarTcgen05},
+    {kOpFwd, kHalfTypes, 256, 256, kVarTcgen05}, {kOpFwd, kAllTypes, 512, 0, kVarGeneral},
+    {kOpBwd, kHalfTypes, 64, 64, kVarTcgen05},   {kOpBwd, kHalfTypes, 128, 128, kVarTcgen05},
+    {kOpBwd, kAllTypes, 512, 0, kVarGeneral},
+};
+
 bool want_sm100(int family) { return family != 1; }
+int family_flags(int family) {
+  return family == 1 ? AB200_SELECT_FORCE_GENERAL : (family == 2 ? AB200_SELECT_FORCE_TCGEN05 : 0);
+}
 // The fused backward is chosen on request only (family 3): on the benchmark shapes the two-kernel
 // backward is faster, because the fp32 atomics of the dQ partials saturate the L2.
 bool want_fused(int family) { return family == 3; }
@@ -155,6 +291,26 @@ int ab200_multiprocessor_count(void* stream) {
   int dev = stream_device(static_cast<cudaStream_t>(stream));
   if (dev < 0) return 0;
   return device_info(dev).sms;
+}
+
+int ab200_select_variant(int op, int dtype, int head_dim_qk, int head_dim_vo, int flags) {
+  if (op != kOpFwd && op != kOpBwd) return -kErrInvalidValue;
+  if (dtype < AB200_DTYPE_FP32 || dtype > AB200_DTYPE_BF16) return -kErrNotSupported;
+  if (head_dim_qk <= 0 || head_dim_vo <= 0) return -kErrInvalidValue;
+  const int dmax = head_dim_qk > head_dim_vo ? head_dim_qk : head_dim_vo;
+  const bool tc_ok = (flags & AB200_SELECT_ALIGNED) && head_dim_qk % 8 == 0 && head_dim_vo % 8 == 0 &&
+                     !(flags & AB200_SELECT_FORCE_GENERAL);
+  for (const SelectionRow& r : kSelection) {
+    if (r.op != op || !((r.dtype_mask >> dtype) & 1u) || dmax > r.dmax) continue;
+    if (r.variant != kVarGeneral && !tc_ok) continue;
+    if (r.variant == kVarGeneral && (flags & AB200_SELECT_FORCE_TCGEN05)) return -kErrNotSupported;
+    int variant = r.variant;
+    if (op == kOpBwd && variant == kVarTcgen05 && (flags & AB200_SELECT_FUSED_REQUESTED) &&
+        !(flags & AB200_SELECT_DBIAS) && r.hd > 64)
+      variant = kVarTcgen05Fused;
+    return variant | (r.hd << 8);
+  }
+  return -kErrNotSupported;      // head dim beyond 512
 }
 
 int ab200_set_kernel_family(int family) {
@@ -178,9 +334,20 @@ unsigned int ab200_kernel_status(int reset) {
 int ab200_stream_check(void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   DeviceGuard guard(st);
-  cudaError_t e = cudaStreamSynchronize(st);
+  cudaError_t e = host().stream_sync(st);
   if (e != cudaSuccess) return (int)e;
   return ab200_kernel_status(0) != 0 ? kErrLaunchFailure : 0;
+}
+
+void ab200_debug_host_calls(int fake_device, int fail_call, int fail_code, int fail_after) {
+  g_fake_device.store(fake_device ? 1 : 0);
+  g_fail_code.store(fail_code);
+  g_fail_after.store(fail_after);
+  g_fail_call.store(fail_call >= 0 && fail_call < kNumHostCalls ? fail_call : -1);
+  for (auto& c : g_call_count) c.store(0);
+}
+uint64_t ab200_debug_host_call_count(int call) {
+  return call >= 0 && call < kNumHostCalls ? g_call_count[call].load() : 0;
 }
 
 void ab200_debug_bounded_wait_test(int drop_copy, unsigned int wait_limit_kcycles) {
@@ -219,11 +386,13 @@ int ab200_attn_fwd(const ab200_attn_fwd_args* a, void* stream) {
 
   const int family = g_family;
   cudaError_t err;
-  if (want_sm100(family) && sm100_fwd_supported(a->prob.dtype, p)) {
+  const int sel = ab200_select_variant(kOpFwd, a->prob.dtype, p.dqk, p.dvo,
+                                       family_flags(family) | (sm100_fwd_supported(a->prob.dtype, p) ? AB200_SELECT_ALIGNED : 0));
+  if (sel < 0) return -sel;
+  if ((sel & 0xff) >= kVarTcgen05) {
     err = launch_sm100_fwd(a->prob.dtype, p, st);
     t_last_fwd = 2;
   } else {
-    if (family == 2) return kErrNotSupported;
     err = launch_general(0, a->prob.dtype, p, st);
     t_last_fwd = 1;
   }
@@ -277,12 +446,13 @@ int ab200_bwd_dkdv(const ab200_attn_bwd_args* a, void* stream) {
   if (!a->dk.ptr || !a->dv.ptr) return kErrInvalidValue;
   if (int e = check_device(st)) return e;
   DeviceGuard guard(st);
-  const int family = g_family;
-  if (want_sm100(family) && sm100_bwd_supported(a->prob.dtype, p)) {
+  const int sel = ab200_select_variant(kOpBwd, a->prob.dtype, p.dqk, p.dvo,
+                                       family_flags(g_family) | (sm100_bwd_supported(a->prob.dtype, p) ? AB200_SELECT_ALIGNED : 0));
+  if (sel < 0) return -sel;
+  if ((sel & 0xff) >= kVarTcgen05) {
     t_last_bwd = 2;
     return (int)launch_sm100_bwd_dkdv(a->prob.dtype, p, st);
   }
-  if (family == 2) return kErrNotSupported;
   t_last_bwd = 1;
   return (int)launch_general(1, a->prob.dtype, p, st);
 }
@@ -294,12 +464,13 @@ int ab200_bwd_dq(const ab200_attn_bwd_args* a, void* stream) {
   if (!a->dq.ptr) return kErrInvalidValue;
   if (int e = check_device(st)) return e;
   DeviceGuard guard(st);
-  const int family = g_family;
-  if (want_sm100(family) && sm100_bwd_supported(a->prob.dtype, p)) {
+  const int sel = ab200_select_variant(kOpBwd, a->prob.dtype, p.dqk, p.dvo,
+                                       family_flags(g_family) | (sm100_bwd_supported(a->prob.dtype, p) ? AB200_SELECT_ALIGNED : 0));
+  if (sel < 0) return -sel;
+  if ((sel & 0xff) >= kVarTcgen05) {
     t_last_bwd = 2;
     return (int)launch_sm100_bwd_dq(a->prob.dtype, p, st);
   }
-  if (family == 2) return kErrNotSupported;
   t_last_bwd = 1;
   return (int)launch_general(2, a->prob.dtype, p, st);
 }
@@ -310,7 +481,10 @@ int ab200_bwd_uses_dq_acc(const ab200_attn_bwd_args* a, void* stream) {
   Params p{};
   if (fill_bwd(a, p, true) != 0 || !a->dq.ptr || !a->dk.ptr || !a->dv.ptr) return 0;
   if (check_device(st) != 0) return 0;
-  return sm100_bwd_fused_supported(a->prob.dtype, p) ? 1 : 0;
+  const int sel = ab200_select_variant(kOpBwd, a->prob.dtype, p.dqk, p.dvo,
+                                       AB200_SELECT_FUSED_REQUESTED | (p.has_dbias ? AB200_SELECT_DBIAS : 0) |
+                                           (sm100_bwd_supported(a->prob.dtype, p) ? AB200_SELECT_ALIGNED : 0));
+  return sel > 0 && (sel & 0xff) == kVarTcgen05Fused && sm100_bwd_fused_supported(a->prob.dtype, p) ? 1 : 0;
 }
 
 int ab200_bwd_fused(const ab200_attn_bwd_args* a, void* stream) {
@@ -365,10 +539,13 @@ float* static_delta_address(int dev, cudaError_t* err) {
   std::lock_guard<std::mutex> lock(mu);
   if (table[dev] == nullptr) {
     int cur = -1;
-    if ((*err = cudaGetDevice(&cur)) != cudaSuccess) return nullptr;
+    if ((*err = host().get_device(&cur)) != cudaSuccess) return nullptr;
     if (cur != dev) { *err = cudaErrorInvalidDevice; return nullptr; }   // symbol lookup is per current device
     float* ptr = nullptr;
-    if ((*err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_delta)) != cudaSuccess) return nullptr;
+    if ((*err = host().symbol_address(reinterpret_cast<void**>(&ptr), reinterpret_cast<const void*>(&g_static_delta))) !=
+        cudaSuccess)
+      return nullptr;
+    if (fake()) return ptr;       // (a pretended device's address is not remembered)
     table[dev] = ptr;
   }
   return table[dev];

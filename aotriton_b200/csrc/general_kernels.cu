@@ -497,7 +497,7 @@ size_t bwd_smem() { return (4 * kTile * (DJ * 32 + kPad) + 2 * kTile * kTile + 2
 template <typename K>
 cudaError_t set_smem(K kernel, size_t bytes) {
   if (bytes <= 48 * 1024) return cudaSuccess;
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  return host().func_set_smem(reinterpret_cast<const void*>(kernel), (int)bytes);
 }
 
 template <typename T, int DJ>
@@ -507,20 +507,20 @@ cudaError_t launch_general_T(int which, const Params& p, cudaStream_t st) {
     size_t sm = fwd_smem<T, DJ>();
     if ((e = set_smem(general_fwd_kernel<T, DJ>, sm)) != cudaSuccess) return e;
     dim3 grid((p.max_sq + kTile - 1) / kTile, p.hq, p.batch);
-    general_fwd_kernel<T, DJ><<<grid, kThreads, sm, st>>>(p);
+    e = launch_kernel(general_fwd_kernel<T, DJ>, dim3(grid), dim3(kThreads), sm, st, p);
   } else if (which == 1) {
     size_t sm = bwd_smem<T, DJ>();
     if ((e = set_smem(general_bwd_dkdv_kernel<T, DJ>, sm)) != cudaSuccess) return e;
     dim3 grid((p.max_sk + kTile - 1) / kTile, p.hk, p.batch);
-    general_bwd_dkdv_kernel<T, DJ><<<grid, kThreads, sm, st>>>(p);
+    e = launch_kernel(general_bwd_dkdv_kernel<T, DJ>, dim3(grid), dim3(kThreads), sm, st, p);
   } else {
     size_t sm = bwd_smem<T, DJ>();
     if ((e = set_smem(general_bwd_dq_kernel<T, DJ>, sm)) != cudaSuccess) return e;
     dim3 grid((p.max_sq + kTile - 1) / kTile, p.hq, p.batch);
-    general_bwd_dq_kernel<T, DJ><<<grid, kThreads, sm, st>>>(p);
+    e = launch_kernel(general_bwd_dq_kernel<T, DJ>, dim3(grid), dim3(kThreads), sm, st, p);
   }
-  count_launch();
-  return cudaGetLastError();
+  if (e == cudaSuccess) count_launch();
+  return e;
 }
 
 template <typename T>
@@ -547,14 +547,15 @@ cudaError_t launch_general(int which, int dtype, const Params& p, cudaStream_t s
 cudaError_t launch_preprocess(int dtype, const Params& p, cudaStream_t st) {
   if (p.max_sq <= 0 || p.batch <= 0) return cudaSuccess;
   dim3 grid((p.max_sq + 127) / 128, p.hq, p.batch);
+  cudaError_t e = cudaSuccess;
   switch (dtype) {
-    case 1: bwd_preprocess_kernel<float><<<grid, 256, 0, st>>>(p); break;
-    case 2: bwd_preprocess_kernel<__half><<<grid, 256, 0, st>>>(p); break;
-    case 3: bwd_preprocess_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p); break;
+    case 1: e = launch_kernel(bwd_preprocess_kernel<float>, dim3(grid), dim3(256), 0, st, p); break;
+    case 2: e = launch_kernel(bwd_preprocess_kernel<__half>, dim3(grid), dim3(256), 0, st, p); break;
+    case 3: e = launch_kernel(bwd_preprocess_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, p); break;
     default: return cudaErrorInvalidValue;
   }
-  count_launch();
-  return cudaGetLastError();
+  if (e == cudaSuccess) count_launch();
+  return e;
 }
 
 cudaError_t launch_postprocess(int dtype, const View4& dq, const float* acc, float scale, cudaStream_t st) {
@@ -565,14 +566,15 @@ cudaError_t launch_postprocess(int dtype, const View4& dq, const float* acc, flo
   const int vec = (dtype != 1) && dq.n[3] % 8 == 0 && (reinterpret_cast<uintptr_t>(dq.ptr) & 15u) == 0 &&
                   dq.s[0] % 8 == 0 && dq.s[1] % 8 == 0 && dq.s[2] % 8 == 0 && dq.s[3] == 1 &&
                   (reinterpret_cast<uintptr_t>(acc) & 15u) == 0;
+  cudaError_t e = cudaSuccess;
   switch (dtype) {
-    case 1: bwd_postprocess_kernel<float><<<grid, 256, 0, st>>>(dq, acc, scale, 0); break;
-    case 2: bwd_postprocess_kernel<__half><<<grid, 256, 0, st>>>(dq, acc, scale, vec); break;
-    case 3: bwd_postprocess_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(dq, acc, scale, vec); break;
+    case 1: e = launch_kernel(bwd_postprocess_kernel<float>, dim3(grid), dim3(256), 0, st, dq, acc, scale, 0); break;
+    case 2: e = launch_kernel(bwd_postprocess_kernel<__half>, dim3(grid), dim3(256), 0, st, dq, acc, scale, vec); break;
+    case 3: e = launch_kernel(bwd_postprocess_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, dq, acc, scale, vec); break;
     default: return cudaErrorInvalidValue;
   }
-  count_launch();
-  return cudaGetLastError();
+  if (e == cudaSuccess) count_launch();
+  return e;
 }
 
 cudaError_t launch_dropout_sign(int dtype, const View4& r, int batch, int heads, int rows, int cols, float dropout_p,
@@ -582,14 +584,15 @@ cudaError_t launch_dropout_sign(int dtype, const View4& r, int batch, int heads,
   d.threshold = dropout_threshold(dropout_p);
   int64_t per = (int64_t)rows * ((cols + 3) / 4);
   dim3 grid((unsigned)((per + 255) / 256), heads, batch);
+  cudaError_t e = cudaSuccess;
   switch (dtype) {
-    case 1: dropout_sign_kernel<float><<<grid, 256, 0, st>>>(r, rows, cols, heads, d, seed, off1, off2); break;
-    case 2: dropout_sign_kernel<__half><<<grid, 256, 0, st>>>(r, rows, cols, heads, d, seed, off1, off2); break;
-    case 3: dropout_sign_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(r, rows, cols, heads, d, seed, off1, off2); break;
+    case 1: e = launch_kernel(dropout_sign_kernel<float>, dim3(grid), dim3(256), 0, st, r, rows, cols, heads, d, seed, off1, off2); break;
+    case 2: e = launch_kernel(dropout_sign_kernel<__half>, dim3(grid), dim3(256), 0, st, r, rows, cols, heads, d, seed, off1, off2); break;
+    case 3: e = launch_kernel(dropout_sign_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, r, rows, cols, heads, d, seed, off1, off2); break;
     default: return cudaErrorInvalidValue;
   }
-  count_launch();
-  return cudaGetLastError();
+  if (e == cudaSuccess) count_launch();
+  return e;
 }
 
 }  // namespace ab200

@@ -1315,19 +1315,22 @@ cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st, float* dq_
   static std::atomic<bool> attr_set[64][5];
   const bool exact = p.varlen_mode == 0 && p.max_sq % 128 == 0 && p.max_sk % 128 == 0 && p.dqk == HD && p.dvo == HD;
   int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
+  cudaError_t e = host().get_device(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  PerDevice& pd = per_device[dev];
+  // (a pretended device, used by host-side tests, gets a scratch record that is never reused)
+  PerDevice scratch;
+  const bool pretend = host_pretends();
+  PerDevice& pd = pretend ? scratch : per_device[dev];
   unsigned int* status = pd.status.load(std::memory_order_acquire);
   if (status == nullptr) {
-    if ((e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_sm100_bwd_status)) != cudaSuccess) return e;
+    if ((e = host().symbol_address(reinterpret_cast<void**>(&status), reinterpret_cast<const void*>(&g_sm100_bwd_status))) != cudaSuccess) return e;
     pd.status.store(status, std::memory_order_release);
   }
   auto set_smem = [&](int slot, const void* fn, int bytes) -> cudaError_t {
-    if (attr_set[dev][slot].load(std::memory_order_acquire)) return cudaSuccess;
-    cudaError_t r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (r == cudaSuccess) attr_set[dev][slot].store(true, std::memory_order_release);
+    if (!pretend && attr_set[dev][slot].load(std::memory_order_acquire)) return cudaSuccess;
+    cudaError_t r = host().func_set_smem(fn, bytes);
+    if (r == cudaSuccess && !pretend) attr_set[dev][slot].store(true, std::memory_order_release);
     return r;
   };
   if (which == 1 || which == 3) {
@@ -1341,7 +1344,7 @@ cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st, float* dq_
     const int nitems = ((p.max_sk + kBlk - 1) / kBlk) * ((p.hk * p.batch + 7) / 8) * 8;
     int sms = pd.sms.load(std::memory_order_acquire);
     if (sms == 0) {
-      if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+      if ((e = host().device_attr(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
       pd.sms.store(sms, std::memory_order_release);
     }
     dim3 grid(nitems < sms ? nitems : sms, 1, 1);     // persistent: one CTA per SM
@@ -1349,24 +1352,26 @@ cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st, float* dq_
     static std::atomic<unsigned int> launch_seq{0};
     unsigned int* tickets = pd.tickets.load(std::memory_order_acquire);
     if (tickets == nullptr) {
-      if ((e = cudaGetSymbolAddress(reinterpret_cast<void**>(&tickets), g_dkdv_ticket)) != cudaSuccess) return e;
+      if ((e = host().symbol_address(reinterpret_cast<void**>(&tickets), reinterpret_cast<const void*>(&g_dkdv_ticket))) != cudaSuccess) return e;
       pd.tickets.store(tickets, std::memory_order_release);
     }
     unsigned int* ticket = tickets + (launch_seq.fetch_add(1) % kTicketPool);
-    if ((e = cudaMemsetAsync(ticket, 0, sizeof(unsigned int), st)) != cudaSuccess) return e;
+    if ((e = host().memset_async(ticket, 0, sizeof(unsigned int), st)) != cudaSuccess) return e;
     if (fused)
-      kern_fused<<<grid, kFusedThreads, BwdSmem<128>::kDynamic, st>>>(p, tq, tk, tv, tdo, status, nitems, ticket, dq_acc);
+      e = launch_kernel(kern_fused, grid, dim3(kFusedThreads), BwdSmem<128>::kDynamic, st, p, tq, tk, tv, tdo, status, nitems,
+                        ticket, dq_acc);
     else
-      kern_split<<<grid, kBwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, tdo, status, nitems, ticket, nullptr);
+      e = launch_kernel(kern_split, grid, dim3(kBwdThreads), L::kDynamic, st, p, tq, tk, tv, tdo, status, nitems, ticket,
+                        static_cast<float*>(nullptr));
   } else {
     auto kern_dq = exact ? sm100_bwd_dq_kernel<T, HD, true> : sm100_bwd_dq_kernel<T, HD, false>;
     e = set_smem(exact ? 4 : 1, reinterpret_cast<const void*>(kern_dq), DqSmem<HD>::kDynamic);
     if (e != cudaSuccess) return e;
     dim3 grid((p.max_sq + kBlk - 1) / kBlk, p.hq, p.batch);
-    kern_dq<<<grid, kBwdThreads, DqSmem<HD>::kDynamic, st>>>(p, tq, tk, tv, tdo, status);
+    e = launch_kernel(kern_dq, grid, dim3(kBwdThreads), DqSmem<HD>::kDynamic, st, p, tq, tk, tv, tdo, status);
   }
-  count_launch();
-  return cudaGetLastError();
+  if (e == cudaSuccess) count_launch();
+  return e;
 }
 
 cudaError_t launch_bwd(int which, int dtype, const Params& p, cudaStream_t st, float* dq_acc) {
@@ -1389,7 +1394,7 @@ bool sm100_bwd_supported(int dtype, const Params& p) {
   if (p.dq.ptr && !vector_store_friendly(p.dq)) return false;
   if (p.dk.ptr && !vector_store_friendly(p.dk)) return false;
   if (p.dv.ptr && !vector_store_friendly(p.dv)) return false;
-  return tensor_map_encoder() != nullptr;
+  return host().have_encoder();
 }
 
 cudaError_t launch_sm100_bwd_dkdv(int dtype, const Params& p, cudaStream_t st) { return launch_bwd(1, dtype, p, st, nullptr); }

@@ -607,24 +607,24 @@ cudaError_t launch_fwd_TE(const Params& p, cudaStream_t st) {
   static std::atomic<unsigned int*> status_of[64];
   static std::atomic<bool> attr_set[64];
   int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
+  cudaError_t e = host().get_device(&dev);
   if (e != cudaSuccess) return e;
-  const bool cached = dev >= 0 && dev < 64;
+  const bool cached = dev >= 0 && dev < 64 && !host_pretends();
   if (!cached || !attr_set[dev].load(std::memory_order_acquire)) {
-    e = cudaFuncSetAttribute(sm100_fwd_kernel<T, HD, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    e = host().func_set_smem(reinterpret_cast<const void*>(sm100_fwd_kernel<T, HD, EXACT>), L::kDynamic);
     if (e != cudaSuccess) return e;
     if (cached) attr_set[dev].store(true, std::memory_order_release);
   }
   unsigned int* status = cached ? status_of[dev].load(std::memory_order_acquire) : nullptr;
   if (status == nullptr) {
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_sm100_fwd_status);
+    e = host().symbol_address(reinterpret_cast<void**>(&status), reinterpret_cast<const void*>(&g_sm100_fwd_status));
     if (e != cudaSuccess) return e;
     if (cached) status_of[dev].store(status, std::memory_order_release);
   }
   dim3 grid((p.max_sq + L::kCtaRows - 1) / L::kCtaRows, p.hq, p.batch);
-  sm100_fwd_kernel<T, HD, EXACT><<<grid, kFwdThreads, L::kDynamic, st>>>(p, tq, tk, tv, status);
-  count_launch();
-  return cudaGetLastError();
+  e = launch_kernel(sm100_fwd_kernel<T, HD, EXACT>, grid, dim3(kFwdThreads), L::kDynamic, st, p, tq, tk, tv, status);
+  if (e == cudaSuccess) count_launch();
+  return e;
 }
 
 template <typename T, int HD>
@@ -642,7 +642,7 @@ bool sm100_fwd_supported(int dtype, const Params& p) {
   // O is written with 16-byte vector stores
   if (!aligned16(p.out.ptr) || p.out.s[0] % 8 != 0 || p.out.s[1] % 8 != 0 || p.out.s[2] % 8 != 0) return false;
   if (p.q.n[3] != p.dqk || p.k.n[3] != p.dqk || p.v.n[3] != p.dvo) return false;
-  return tensor_map_encoder() != nullptr;
+  return host().have_encoder();
 }
 
 cudaError_t launch_sm100_fwd(int dtype, const Params& p, cudaStream_t st) {

@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include "common.cuh"
+#include "launch.h"
 
 namespace ab200 {
 namespace ptx {
@@ -417,23 +418,8 @@ inline bool vector_store_friendly(const View4& v) {
   return v.ptr != nullptr && aligned16(v.ptr) && v.s[0] % 8 == 0 && v.s[1] % 8 == 0 && v.s[2] % 8 == 0 && v.s[3] == 1;
 }
 
-// ---- host side: TMA descriptor encoding without linking libcuda ----------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-inline EncodeTiledFn tensor_map_encoder() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
+// ---- host side: TMA descriptor encoding goes through the host-call table (launch.h), which looks
+// the driver's encoder up at run time, so that the library does not link libcuda.
 // ---- write-out of a [128 rows x D] 16-bit tile through shared memory -----------------------
 // A thread that owns one row of a tile (a TMEM lane) would store 16 bytes per instruction at a
 // row stride: 32 separate memory lines per warp instruction, which costs thousands of cycles per
@@ -481,8 +467,6 @@ __device__ __forceinline__ void warp_copy_out(const uint8_t* stage, T* tile, int
 // Tile map over a (B, H, S, D) view of 16-bit elements: box = 64 columns x `box_rows` rows,
 // 128-byte swizzle, zero fill outside the extents.  Dimensions are given innermost first.
 inline bool make_tile_map_16bit(CUtensorMap* out, const View4& v, int64_t d_extent, int64_t s_extent, int box_rows) {
-  EncodeTiledFn enc = tensor_map_encoder();
-  if (!enc) return false;
   cuuint64_t dims[4] = {(cuuint64_t)d_extent, (cuuint64_t)s_extent, (cuuint64_t)v.n[1], (cuuint64_t)v.n[0]};
   cuuint64_t strides[3] = {(cuuint64_t)v.s[2] * 2, (cuuint64_t)v.s[1] * 2, (cuuint64_t)v.s[0] * 2};
   // A unit extent may carry any stride; give it a legal one.
@@ -490,10 +474,10 @@ inline bool make_tile_map_16bit(CUtensorMap* out, const View4& v, int64_t d_exte
     if (dims[i + 1] == 1 && (strides[i] == 0 || strides[i] % 16 != 0)) strides[i] = 16;
   cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, v.ptr, dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  const int r = host().encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, v.ptr, dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == 0;
 }
 
 }  // namespace ab200

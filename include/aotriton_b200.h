@@ -202,8 +202,25 @@ AB200_API int ab200_multiprocessor_count(void* stream);
  * Per calling thread.  Returns the old value. */
 AB200_API int ab200_set_kernel_family(int family);
 
+/* The static selection table, the counterpart of the reference's tuning-database lookup
+ * (v3src/flash/autotune.*: tables FLASH$op_attn_fwd / FLASH$op_attn_bwd keyed by dtype, head-dim
+ * bin, bias, dropout, causal and sequence-length bins).  op: 0 forward, 1 backward; flags: OR of
+ * the AB200_SELECT_* bits.  Returns variant | (head-dim instantiation << 8) with variant
+ * 1 = general kernels, 2 = tcgen05 kernels, 3 = tcgen05 kernels with the fused backward, or the
+ * negated error code (hipErrorNotSupported for a head dim beyond 512 or when tcgen05 kernels were
+ * required but cannot take the problem).  Pure function: needs no device. */
+enum {
+  AB200_SELECT_ALIGNED = 1,          /* tensors are 16-byte aligned with unit inner stride        */
+  AB200_SELECT_DBIAS = 2,            /* backward: dBias requested                                 */
+  AB200_SELECT_FUSED_REQUESTED = 4,  /* backward: family 3, dq_acc given, deterministic == 0      */
+  AB200_SELECT_FORCE_GENERAL = 8,    /* kernel family 1                                           */
+  AB200_SELECT_FORCE_TCGEN05 = 16    /* kernel family 2                                           */
+};
+AB200_API int ab200_select_variant(int op, int dtype, int head_dim_qk, int head_dim_vo, int flags);
+
 /* Which family the most recent forward / backward launch of this thread used
- * (1 = general, 2 = tcgen05); diagnostics for tests and benchmarks. */
+ * (1 = general, 2 = tcgen05, 3 = tcgen05 with the fused backward); diagnostics for tests and
+ * benchmarks. */
 AB200_API int ab200_last_fwd_family(void);
 AB200_API int ab200_last_bwd_family(void);
 
@@ -231,6 +248,18 @@ AB200_API int ab200_stream_check(void* stream);
  * runs out, the kernel records which one and returns normally.  Nothing faults or hangs:
  * the kernel takes a few limits to drain.  Call with (0, 0) to restore normal operation. */
 AB200_API void ab200_debug_bounded_wait_test(int drop_copy, unsigned int wait_limit_kcycles);
+
+/* Test hooks for the host side of the launch path; no counterpart in the reference.  Every CUDA
+ * call the library makes on that path goes through one table.  fake_device != 0 makes the table
+ * pretend an sm_100 device (148 SMs): device queries answer, symbol look-ups, attribute settings
+ * and kernel launches are counted and skipped, so the whole host logic runs on a machine without
+ * a GPU.  fail_call >= 0 makes the (fail_after + 1)-th call of that entry return fail_code
+ * instead of doing anything: 0 get-device, 1 set-device, 2 stream-device, 3 device-attribute,
+ * 4 function-attribute, 5 symbol-address, 6 memset, 7 kernel launch, 8 tensor-map encoder,
+ * 9 stream-synchronise.  Resets the per-entry call counters.  (0, -1, 0, 0) restores normal
+ * operation.  Process-wide; meant for single-threaded tests.  Nothing here touches a device. */
+AB200_API void ab200_debug_host_calls(int fake_device, int fail_call, int fail_code, int fail_after);
+AB200_API uint64_t ab200_debug_host_call_count(int call);
 
 /* Number of kernels launched by this library since load (all threads). */
 AB200_API uint64_t ab200_launch_count(void);

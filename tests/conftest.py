@@ -2,7 +2,12 @@ import os
 import sys
 from pathlib import Path
 
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
 import pytest
+
+# one GPU per pytest-xdist worker (`pytest -n 8 -m gpu` on a multi-GPU box); a no-op otherwise
+pytest_plugins = ["aotriton_b200.testing.gpu_lease"]
 
 ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:

@@ -42,7 +42,8 @@ int main(void) {
          offsetof(ab200_attn_problem, philox_num_head_q));
   printf("%zu %zu %zu ", offsetof(ab200_attn_fwd_args, lse), offsetof(ab200_attn_fwd_args, encoded_softmax_cols),
          offsetof(ab200_attn_fwd_args, persistent_atomic_counter));
-  printf("%zu %zu\n", offsetof(ab200_attn_bwd_args, dbias), offsetof(ab200_attn_bwd_args, deterministic));
+  printf("%zu %zu %zu\n", offsetof(ab200_attn_bwd_args, dbias), offsetof(ab200_attn_bwd_args, deterministic),
+         offsetof(ab200_attn_bwd_args, dq_acc));
   return 0;
 }
 """)
@@ -53,7 +54,7 @@ int main(void) {
             ctypes.sizeof(cabi.BwdArgs), cabi.Problem.cu_seqlens_q.offset, cabi.Problem.philox_offset2.offset,
             cabi.Problem.philox_num_head_q.offset, cabi.FwdArgs.lse.offset,
             cabi.FwdArgs.encoded_softmax_cols.offset, cabi.FwdArgs.persistent_atomic_counter.offset,
-            cabi.BwdArgs.dbias.offset, cabi.BwdArgs.deterministic.offset]
+            cabi.BwdArgs.dbias.offset, cabi.BwdArgs.deterministic.offset, cabi.BwdArgs.dq_acc.offset]
     assert got == want
 
 

@@ -138,3 +138,41 @@ def test_varlen_partition_and_philox_adjustment():
     adj = sharding.philox_adjustment(sharding.Segment(2, 3, 5), group=4, num_head_q=32, max_seqlen_q=100,
                                      max_seqlen_k=50)
     assert adj == dict(philox_offset2_add=2 * 32 * 100 * 13, philox_head_offset=12, philox_num_head_q=32)
+
+
+def test_custom_ops_trace_without_a_device():
+    """The torch.library operators carry fake implementations and an autograd formula, so a tracer sees
+    shapes and dtypes without any kernel (and without a GPU)."""
+    import torch
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from aotriton_b200 import autograd
+    with FakeTensorMode():
+        q = torch.empty(2, 8, 128, 64, dtype=torch.bfloat16, device="cuda", requires_grad=True)
+        k = torch.empty(2, 2, 128, 64, dtype=torch.bfloat16, device="cuda", requires_grad=True)
+        v = torch.empty(2, 2, 128, 96, dtype=torch.bfloat16, device="cuda", requires_grad=True)
+        o = autograd.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        assert o.shape == (2, 8, 128, 96) and o.dtype == torch.bfloat16
+        o.sum().backward()
+        assert q.grad.shape == q.shape and k.grad.shape == k.shape and v.grad.shape == v.shape
+    for bad in (dict(attn_mask=torch.zeros(1, dtype=torch.bool)), dict(attn_mask=torch.zeros(1), is_causal=True)):
+        try:
+            autograd.scaled_dot_product_attention(torch.zeros(1, 1, 4, 8), torch.zeros(1, 1, 4, 8),
+                                                  torch.zeros(1, 1, 4, 8), **bad)
+            raise AssertionError("accepted an unsupported mask")
+        except ValueError:
+            pass
+
+
+def test_bench_traffic_table_equals_the_profile_summary():
+    """roofline.traffic comes from one table in bench.py; it must quote the committed ncu summary."""
+    import importlib.util
+    import re
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    spec = importlib.util.spec_from_file_location("bench_module", root / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    text = (root / "profiles" / "tcgen05_kernels_dense_causal_bf16_B2_H32_S4096_D128.md").read_text()
+    numbers = {float(x) for x in re.findall(r"(\d+\.\d+)\s*MB", text)}
+    for kern, (rd, wr) in bench.C2_DRAM_TRAFFIC_B2.items():
+        assert rd / 1e6 in numbers and wr / 1e6 in numbers, (kern, rd, wr, sorted(numbers))
