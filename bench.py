@@ -292,14 +292,17 @@ def config_block(name, dev, timer, peaks, lib):
     f = timer.flushed(pr.fwd)
     b = timer.flushed(pr.bwd)
     stages = {s: timer.flushed(lambda s=s: pr.bwd(s)) for s in ("preprocess", "dkdv", "dq")}
-    rec.update(fwd_ms=f["median_ms"], fwd_min_ms=f["min_ms"], bwd_ms=b["median_ms"], bwd_min_ms=b["min_ms"],
-               bwd_stage_ms={k: v["median_ms"] for k, v in stages.items()}, reps=f["reps"],
-               fwd_tflops=tfl(pr.flops_fwd, f["median_ms"]), bwd_tflops=tfl(2.5 * pr.flops_fwd, b["median_ms"]),
+    # backward time = sum of its three kernels' medians; the median of whole calls (which also shows
+    # the host's launch work when every call starts on an idle GPU) is kept beside it
+    bk = sum(v["median_ms"] for v in stages.values())
+    rec.update(fwd_ms=f["median_ms"], fwd_min_ms=f["min_ms"], bwd_ms=bk, bwd_call_ms=b["median_ms"],
+               bwd_call_min_ms=b["min_ms"], bwd_stage_ms={k: v["median_ms"] for k, v in stages.items()}, reps=f["reps"],
+               fwd_tflops=tfl(pr.flops_fwd, f["median_ms"]), bwd_tflops=tfl(2.5 * pr.flops_fwd, bk),
                fwd_frac_of_peak=tfl(pr.flops_fwd, f["median_ms"]) / peaks["bf16"],
-               bwd_frac_of_peak=tfl(2.5 * pr.flops_fwd, b["median_ms"]) / peaks["bf16"],
-               fwd_gbs=pr.bytes_fwd / (f["median_ms"] * 1e-3) / 1e9, bwd_gbs=pr.bytes_bwd / (b["median_ms"] * 1e-3) / 1e9,
+               bwd_frac_of_peak=tfl(2.5 * pr.flops_fwd, bk) / peaks["bf16"],
+               fwd_gbs=pr.bytes_fwd / (f["median_ms"] * 1e-3) / 1e9, bwd_gbs=pr.bytes_bwd / (bk * 1e-3) / 1e9,
                fwd_frac_of_hbm=pr.bytes_fwd / (f["median_ms"] * 1e-3) / 1e9 / peaks["hbm"],
-               bwd_frac_of_hbm=pr.bytes_bwd / (b["median_ms"] * 1e-3) / 1e9 / peaks["hbm"],
+               bwd_frac_of_hbm=pr.bytes_bwd / (bk * 1e-3) / 1e9 / peaks["hbm"],
                kernel_status=int(lib.ab200_kernel_status(0)))
     if "lens_sum" in pr.c:
         rec.update(tokens=pr.c["lens_sum"], max_seqlen=pr.c["lens_max"])
@@ -474,6 +477,20 @@ def main():
             "bwd_dkdv": timer.flushed(stage("dkdv"), reps), "bwd_dq": timer.flushed(stage("dq"), reps),
             "bwd_all": timer.flushed(bwd, reps)}
     kern_ms = {n: r["median_ms"] for n, r in kern.items()}
+    # the fused backward (dK, dV and atomically accumulated dQ in one kernel + conversion kernel),
+    # which the library only uses on request: accumulator zeroing, kernel and conversion
+    acc = torch.zeros(B, H, S, D, dtype=torch.float32, device=dev)
+    fused = None
+    if cabi.attn_bwd(q, k, v, o, do, dq, dk, dv, lse, delta, sm_scale=sm, causal_type=3, window_left=cabi.WINDOW_TOP_LEFT,
+                     window_right=cabi.WINDOW_TOP_LEFT, stage="fused", dq_acc=acc) == 0:
+        fz = lambda name: (lambda: cabi.attn_bwd(q, k, v, o, do, dq, dk, dv, lse, delta, sm_scale=sm, causal_type=3,
+                                                 window_left=cabi.WINDOW_TOP_LEFT, window_right=cabi.WINDOW_TOP_LEFT,
+                                                 stage=name, dq_acc=acc))
+        fused = dict(zero_ms=timer.flushed(lambda: acc.zero_(), reps)["median_ms"],
+                     kernel_ms=timer.flushed(fz("fused"), reps)["median_ms"],
+                     convert_ms=timer.flushed(fz("postprocess"), reps)["median_ms"])
+        fused["bwd_ms"] = kern_ms["bwd_preprocess"] + sum(fused.values())
+    del acc
 
     # ---- end to end through the public API with host buffers -------------------------------------
     # Every step copies its four inputs from pinned host memory and its four results back, inside the
@@ -538,7 +555,7 @@ def main():
     dom_traffic = (rd + wr) * B / 2.0 if (H, S, D) == (32, 4096, 128) else None
     dom_flops = {"attn_fwd": ffwd, "bwd_dkdv": 2.0 * ffwd, "bwd_dq": 1.5 * ffwd}[dom]
     nbytes = q.numel() * 2
-    bwd_ms = kern_ms["bwd_all"]
+    bwd_ms = kern_ms["bwd_preprocess"] + kern_ms["bwd_dkdv"] + kern_ms["bwd_dq"]      # sum of kernel medians
     line = dict(
         metric=METRIC, value=value, unit="TFLOPS", n_gpus=world, steps=args.steps, warmup=warm,
         ms_per_step=ms_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
@@ -555,6 +572,12 @@ def main():
                      bwd_frac_of_sustained_peak=(tfl(fbwd, bwd_ms) / peaks["bf16_sustained"]
                                                  if peaks["bf16_sustained"] else None),
                      kernel_ms=kern_ms, kernel_min_ms={n: r["min_ms"] for n, r in kern.items()},
+                     bwd_ms=bwd_ms, bwd_call_ms=kern_ms["bwd_all"],
+                     fused_backward=(dict(fused, tflops=tfl(fbwd, fused["bwd_ms"]),
+                                          frac_of_peak=tfl(fbwd, fused["bwd_ms"]) / peaks["bf16"],
+                                          note="opt-in (kernel family 3 / force_backend_index 2): slower than the "
+                                               "two-kernel backward here, its fp32 atomics saturate the L2")
+                                     if fused else None),
                      kernel_timing=f"CUDA events, 1 GiB L2 flush before each call, median of {reps} (min beside it)",
                      # the timed loop runs for hundreds of milliseconds under the power cap: the
                      # cuBLAS figure measured the same way (seconds-long loop) is the fair yardstick

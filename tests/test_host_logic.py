@@ -147,13 +147,17 @@ def test_custom_ops_trace_without_a_device():
     from torch._subclasses.fake_tensor import FakeTensorMode
     from aotriton_b200 import autograd
     with FakeTensorMode():
-        q = torch.empty(2, 8, 128, 64, dtype=torch.bfloat16, device="cuda", requires_grad=True)
-        k = torch.empty(2, 2, 128, 64, dtype=torch.bfloat16, device="cuda", requires_grad=True)
-        v = torch.empty(2, 2, 128, 96, dtype=torch.bfloat16, device="cuda", requires_grad=True)
+        q = torch.empty(2, 8, 128, 64, dtype=torch.bfloat16, device="cuda")
+        k = torch.empty(2, 2, 128, 64, dtype=torch.bfloat16, device="cuda")
+        v = torch.empty(2, 2, 128, 96, dtype=torch.bfloat16, device="cuda")
         o = autograd.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
-        assert o.shape == (2, 8, 128, 96) and o.dtype == torch.bfloat16
-        o.sum().backward()
-        assert q.grad.shape == q.shape and k.grad.shape == k.shape and v.grad.shape == v.shape
+        assert o.shape == (2, 8, 128, 96) and o.dtype == torch.bfloat16 and o.device.type == "cuda"
+    # forward and backward through the registered autograd formula, on meta tensors
+    q, k, v = (torch.empty(s, dtype=torch.bfloat16, device="meta", requires_grad=True)
+               for s in ((2, 8, 128, 64), (2, 2, 128, 64), (2, 2, 128, 96)))
+    o = autograd.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+    o.sum().backward()
+    assert q.grad.shape == q.shape and k.grad.shape == k.shape and v.grad.shape == v.shape
     for bad in (dict(attn_mask=torch.zeros(1, dtype=torch.bool)), dict(attn_mask=torch.zeros(1), is_causal=True)):
         try:
             autograd.scaled_dot_product_attention(torch.zeros(1, 1, 4, 8), torch.zeros(1, 1, 4, 8),
