@@ -381,6 +381,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="all", choices=["all", "none"] + sorted(CONFIGS),
                     help="which configurations the `configs` block measures beside the C2 headline (1 GPU)")
+    ap.add_argument("--only-config", default=None, choices=sorted(CONFIGS),
+                    help="run just this configuration's forward and backward three times and print their times "
+                         "(a short, exactly known launch sequence for profiler captures); no headline")
+    ap.add_argument("--config-batch", type=int, default=None,
+                    help="batch size override for --only-config (dense configurations)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiler captures)")
     ap.add_argument("--batch", type=int, default=CONFIGS["c2"]["B"],
@@ -404,6 +409,18 @@ def main():
     from aotriton_b200 import cabi, flash
     from aotriton_b200.flash import hipError_t
     lib = cabi.lib()
+
+    if args.only_config:
+        pr = Problem(args.only_config, torch.device("cuda", local), batch=args.config_batch)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        for _ in range(3):
+            ev[0].record(); pr.fwd(); ev[1].record(); pr.bwd(); ev[2].record()
+        torch.cuda.synchronize()
+        print(json.dumps(dict(only_config=args.only_config, workload=pr.c["desc"], batch=pr.c.get("B"),
+                              fwd_ms=ev[0].elapsed_time(ev[1]), bwd_ms=ev[1].elapsed_time(ev[2]),
+                              fwd_family=lib.ab200_last_fwd_family(), bwd_family=lib.ab200_last_bwd_family(),
+                              kernel_status=int(lib.ab200_kernel_status(0)))), flush=True)
+        return
 
     c2 = CONFIGS["c2"]
     B, H, S, D = args.batch, c2["Hq"], c2["S"], c2["D"]
