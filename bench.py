@@ -60,7 +60,7 @@ CONFIGS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch (bytes) of the C2 kernels, from the ncu
 # capture at batch 2 summarised in profiles/tcgen05_kernels_dense_causal_bf16_B2_H32_S4096_D128.md;
 # per-(batch, head) work is independent, so a launch at batch B moves B/2 times as much.
-C2_DRAM_TRAFFIC_B2 = {"attn_fwd": (201.5e6, 51.7e6), "bwd_dkdv": (275.3e6, 118.7e6), "bwd_dq": (270.6e6, 54.8e6)}
+C2_DRAM_TRAFFIC_B2 = {"attn_fwd": (296.3e6, 49.0e6), "bwd_dkdv": (275.0e6, 117.4e6), "bwd_dq": (270.7e6, 54.8e6)}
 
 
 def measured_peaks():
