@@ -635,7 +635,7 @@ def main():
                                      bwd_frac_of_peak=tfl(fbwd, bwd_ms) / peaks["bf16"],
                                      fwd_family=line["per_gpu"]["fwd_family"], bwd_family=line["per_gpu"]["bwd_family"])
     if rank == 0:
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             units = 8
             val, secs = cpu_sample(units)
             line["cpu_baseline"] = cpu_baseline_record(units, val, secs)
