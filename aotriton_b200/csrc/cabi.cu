@@ -267,7 +267,7 @@ constexpr SelectionRow kSelection[] = {
     {kOpFwd, kHalfTypes, 64, 64, kVarTcgen05},   {kOpFwd, kHalfTypes, 128, 128, kVarTcgen05},
     {kOpFwd, kHalfTypes, 256, 256, kVarTcgen05}, {kOpFwd, kAllTypes, 512, 0, kVarGeneral},
     {kOpBwd, kHalfTypes, 64, 64, kVarTcgen05},   {kOpBwd, kHalfTypes, 128, 128, kVarTcgen05},
-    {kOpBwd, kAllTypes, 512, 0, kVarGeneral},
+    {kOpBwd, kHalfTypes, 256, 256, kVarTcgen05}, {kOpBwd, kAllTypes, 512, 0, kVarGeneral},
 };
 
 bool want_sm100(int family) { return family != 1; }
@@ -306,7 +306,7 @@ int ab200_select_variant(int op, int dtype, int head_dim_qk, int head_dim_vo, in
     if (r.variant == kVarGeneral && (flags & AB200_SELECT_FORCE_TCGEN05)) return -kErrNotSupported;
     int variant = r.variant;
     if (op == kOpBwd && variant == kVarTcgen05 && (flags & AB200_SELECT_FUSED_REQUESTED) &&
-        !(flags & AB200_SELECT_DBIAS) && r.hd > 64)
+        !(flags & AB200_SELECT_DBIAS) && r.hd == 128)
       variant = kVarTcgen05Fused;
     return variant | (r.hd << 8);
   }

@@ -1374,7 +1374,13 @@ cudaError_t launch_bwd_T(int which, const Params& p, cudaStream_t st, float* dq_
   return e;
 }
 
+#include "sm100_bwd_wide.cuh"
+
 cudaError_t launch_bwd(int which, int dtype, const Params& p, cudaStream_t st, float* dq_acc) {
+  if (p.dqk > 128 || p.dvo > 128) {      // wide heads: one launch per gradient (sm100_bwd_wide.cuh)
+    if (which == 3) return cudaErrorInvalidValue;
+    return dtype == 2 ? launch_bwd_wide_T<__half>(which, p, st) : launch_bwd_wide_T<__nv_bfloat16>(which, p, st);
+  }
   const bool small = p.dqk <= 64 && p.dvo <= 64 && which != 3;
   if (dtype == 2)
     return small ? launch_bwd_T<__half, 64>(which, p, st, dq_acc) : launch_bwd_T<__half, 128>(which, p, st, dq_acc);
@@ -1386,7 +1392,7 @@ cudaError_t launch_bwd(int which, int dtype, const Params& p, cudaStream_t st, f
 
 bool sm100_bwd_supported(int dtype, const Params& p) {
   if (dtype != 2 && dtype != 3) return false;
-  if (p.dqk > 128 || p.dvo > 128 || p.dqk % 8 != 0 || p.dvo % 8 != 0) return false;
+  if (p.dqk > 256 || p.dvo > 256 || p.dqk % 8 != 0 || p.dvo % 8 != 0) return false;
   if (p.max_sq <= 0 || p.max_sk <= 0 || p.batch <= 0) return false;
   if (!tma_friendly(p.q) || !tma_friendly(p.k) || !tma_friendly(p.v) || !tma_friendly(p.dout)) return false;
   if (p.q.n[3] != p.dqk || p.k.n[3] != p.dqk || p.v.n[3] != p.dvo || p.dout.n[3] != p.dvo) return false;
@@ -1405,6 +1411,7 @@ cudaError_t launch_sm100_bwd_dq(int dtype, const Params& p, cudaStream_t st) { r
 bool sm100_bwd_fused_supported(int dtype, const Params& p) {
   if (!sm100_bwd_supported(dtype, p)) return false;
   if (p.has_dbias) return false;
+  if (p.dqk > 128 || p.dvo > 128) return false;      // neither have the kernels for wide heads
   if (p.dqk <= 64 && p.dvo <= 64) return false;      // the 64-wide instantiation has no fused form
   return p.dq.ptr != nullptr;
 }

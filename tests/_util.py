@@ -77,9 +77,9 @@ def expected_family(dtype, d_qk: int, d_vo: int, which: str = "fwd", fused: bool
     backward reports 3 when it ran the fused form (dQ accumulator given, head dim above 64, no dBias)."""
     if dtype not in (torch.float16, torch.bfloat16):
         return 1
-    dmax = 256 if which == "fwd" else 128      # the forward has a 256-wide instantiation, the backward not
-    if d_qk > dmax or d_vo > dmax or d_qk % 8 or d_vo % 8:
+    if d_qk > 256 or d_vo > 256 or d_qk % 8 or d_vo % 8:
         return 1
-    if which == "bwd" and fused and not dbias and (d_qk > 64 or d_vo > 64):
+    # the fused form exists for the 128-wide instantiation only
+    if which == "bwd" and fused and not dbias and 64 < max(d_qk, d_vo) <= 128:
         return 3
     return 2

@@ -104,6 +104,12 @@ CASES = [
     (torch.bfloat16, 1, 2, 2, 300, 100, 128, 128, (3, BR, BR), 0.0, False),
     # sliding window over several key blocks: the two query tiles of a CTA reach different blocks
     (torch.float16, 1, 2, 1, 700, 700, 64, 64, (3, 130, 20), 0.0, False),
+    # head dims above 128 (the backward's one-accumulator kernels): GQA with a window over several
+    # 64-row blocks and ragged ends; bottom-right causal with dead rows and dropout; unequal head dims
+    (torch.bfloat16, 2, 4, 2, 300, 420, 192, 192, (3, 100, 30), 0.0, False),
+    (torch.float16, 1, 2, 2, 257, 129, 256, 256, (3, BR, BR), 0.1, False),
+    (torch.bfloat16, 1, 2, 1, 384, 384, 256, 136, (3, TL, TL), 0.0, False),
+    (torch.float16, 1, 3, 3, 200, 333, 160, 160, (0, 0, 0), 0.3, True),
 ]
 
 
@@ -155,6 +161,8 @@ def test_dense_vs_oracle(case, family, dist):
     (torch.float16, 128, 4, 2, 0.1, True),
     (torch.bfloat16, 64, 2, 2, 0.0, False),
     (torch.float16, 32, 3, 3, 0.5, True),
+    (torch.bfloat16, 256, 4, 2, 0.1, True),
+    (torch.float16, 192, 2, 2, 0.0, False),
 ])
 def test_compact_varlen_vs_oracle(family, dt, D, Hq, Hk, p, causal):
     lens = [4, 8, 63, 64, 128, 143, 0, 200, 1]

@@ -134,7 +134,7 @@ def _valid_equal(tag, a, b, dt):
 
 @pytest.mark.parametrize("family", ["general", "sm100"])
 @pytest.mark.parametrize("poison", [float("nan"), float("inf")])
-@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("D", [64, 128, 256])
 def test_padded_varlen_ignores_nonfinite_padding(family, poison, D):
     from aotriton_b200 import cabi
     dt, Hq, Hk = torch.float16, 4, 2
@@ -169,11 +169,12 @@ def test_padded_varlen_ignores_nonfinite_padding(family, poison, D):
 
 @pytest.mark.parametrize("family", ["general", "sm100"])
 @pytest.mark.parametrize("poison", [float("nan"), float("inf")])
-def test_compact_and_strided_varlen_ignore_nonfinite_neighbours(family, poison):
+@pytest.mark.parametrize("D", [128, 192])
+def test_compact_and_strided_varlen_ignore_nonfinite_neighbours(family, poison, D):
     """Compact: one whole sequence holds non-finite tokens; its neighbours, whose last partial blocks
     reach into it, must be unaffected.  Strided: the gaps between sequences hold non-finite values."""
     from aotriton_b200 import cabi
-    dt, Hq, Hk, D = torch.bfloat16, 2, 2, 128
+    dt, Hq, Hk = torch.bfloat16, 2, 2
     lens = [100, 60, 135, 5]
     cu_l = [0] + list(np.cumsum(lens))
     T = cu_l[-1]
@@ -215,14 +216,16 @@ def test_compact_and_strided_varlen_ignore_nonfinite_neighbours(family, poison):
 
 
 # ----------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("which,lo,hi", [(1, 0x100, 0x1000), (2, 0x1000, 0x2000), (3, 0x2000, 0x3000)])
-def test_bounded_wait_runs_out_cleanly(which, lo, hi):
+@pytest.mark.parametrize("which,lo,hi,D", [(1, 0x100, 0x1000, 128), (2, 0x1000, 0x2000, 128), (3, 0x2000, 0x3000, 128),
+                                           (2, 0x3000, 0x4000, 256), (3, 0x3000, 0x4000, 256)])
+def test_bounded_wait_runs_out_cleanly(which, lo, hi, D):
     """One copy is left out on a one-tile problem with a wait limit of about a million cycles: the
     role waiting longest gives up, the kernel drains and returns, and the status word names a wait
-    of the right kernel (forward 0x1xx-0x9xx, dK/dV 0x1xxx, dQ 0x2xxx)."""
+    of the right kernel (forward 0x1xx-0x9xx, dK/dV 0x1xxx, dQ 0x2xxx, the kernels for head dims
+    above 128 0x3xxx)."""
     from aotriton_b200 import cabi
     L = cabi.lib()
-    dt, S, D = torch.bfloat16, 128, 128
+    dt, S = torch.bfloat16, 128
     q, k, v, do = (t.cuda() for t in randn_inputs((1, 1, S, D), (1, 1, S, D), (1, 1, S, D), dt, seed=1))
     out = torch.empty_like(q)
     lse = torch.empty(1, S, dtype=torch.float32, device="cuda")

@@ -175,7 +175,9 @@ def test_selection_table():
     assert unpack(sel(0, cabi.DTYPE_FP16, 72, 72, A)) == (2, 128)
     assert unpack(sel(0, cabi.DTYPE_FP16, 40, 64, A)) == (2, 64)
     assert unpack(sel(0, cabi.DTYPE_FP16, 256, 256, A)) == (2, 256)
-    assert unpack(sel(1, cabi.DTYPE_FP16, 256, 256, A)) == (1, 0)            # no 256-wide backward on tcgen05
+    assert unpack(sel(1, cabi.DTYPE_FP16, 256, 256, A)) == (2, 256)
+    assert unpack(sel(1, cabi.DTYPE_FP16, 256, 256, A | FU)) == (2, 256)     # the fused form is 128-wide only
+    assert unpack(sel(1, cabi.DTYPE_FP16, 264, 264, A)) == (1, 0)
     assert unpack(sel(0, cabi.DTYPE_FP32, 64, 64, A)) == (1, 0)
     assert unpack(sel(0, cabi.DTYPE_BF16, 128, 128, 0)) == (1, 0)            # unaligned tensors
     assert unpack(sel(0, cabi.DTYPE_BF16, 100, 100, A)) == (1, 0)            # head dim not a multiple of 8
