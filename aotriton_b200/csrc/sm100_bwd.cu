@@ -156,6 +156,51 @@ __device__ __forceinline__ void store_row_chunk32(T* dst, const float* v, float 
   }
 }
 
+// Bias of a key-per-thread kernel.  A warp owns 32 keys (one per lane) x 32 query rows of the score
+// tile, i.e. a 32 x 32 tile of the bias matrix whose rows (queries) are 64 contiguous bytes.  A
+// thread needs a COLUMN of it; reading that directly takes 32 two-byte loads per thread at a row
+// stride.  Instead the warp reads the tile with four 16-byte loads per thread (load t: lane 8q+e
+// reads keys 8q..8q+7 of query row 8t+e) and transposes it in registers: within each group of
+// eight lanes an 8 x 8 transpose of 16-bit values, three exchange steps (lane bit <-> position bit).
+// Adds bias * log2(e) to pr[c] (c = query row in the tile).  `tile` points at (first query row,
+// first key of the warp); rows are `row_stride` elements apart and 16-byte aligned.
+template <typename T>
+__device__ __forceinline__ void add_bias_column32(float* pr, const T* tile, int64_t row_stride, int lane) {
+  const int q = lane >> 3, e = lane & 7;
+  uint4 raw[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) raw[t] = __ldg(reinterpret_cast<const uint4*>(tile + (int64_t)(8 * t + e) * row_stride + 8 * q));
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    uint32_t w[4] = {raw[t].x, raw[t].y, raw[t].z, raw[t].w};
+    // lane bit 0 <-> low/high half
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t o = __shfl_xor_sync(0xffffffffu, w[k], 1);
+      w[k] = (lane & 1) ? __byte_perm(w[k], o, 0x3276) : __byte_perm(w[k], o, 0x5410);
+    }
+    // lane bit 1 <-> register index bit 0, lane bit 2 <-> register index bit 1
+#pragma unroll
+    for (int k = 0; k < 4; k += 2) {
+      const bool up = (lane & 2) != 0;
+      const uint32_t got = __shfl_xor_sync(0xffffffffu, up ? w[k] : w[k + 1], 2);
+      if (up) w[k] = got; else w[k + 1] = got;
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const bool up = (lane & 4) != 0;
+      const uint32_t got = __shfl_xor_sync(0xffffffffu, up ? w[k] : w[k + 2], 4);
+      if (up) w[k] = got; else w[k + 2] = got;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const T* h = reinterpret_cast<const T*>(&w[k]);
+      pr[8 * t + 2 * k] = fmaf(to_f32<T>(h[0]), kLog2e, pr[8 * t + 2 * k]);
+      pr[8 * t + 2 * k + 1] = fmaf(to_f32<T>(h[1]), kLog2e, pr[8 * t + 2 * k + 1]);
+    }
+  }
+}
+
 template <typename T>
 __device__ void zero_rows(const View4& v, int b, int h, int64_t tok0, int row0, int nrows, int d) {
   for (int r = threadIdx.x; r < kBlk; r += blockDim.x) {
@@ -698,7 +743,12 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           }
 #pragma unroll
           for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
-          if (p.has_bias && n < sq.sk) {
+          if (p.has_bias && p.bias_vec && mbase + 32 <= sq.sq && it.n0 + quarter * 32 + 32 <= sq.sk) {
+            // the warp's whole 32 x 32 bias tile is inside the sequence: vector loads and a transpose
+            add_bias_column32<T>(pr, reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
+                                         (int64_t)h * p.bias.s[1] + (int64_t)mbase * p.bias.s[2] + (it.n0 + quarter * 32),
+                                 p.bias.s[2], lane);
+          } else if (p.has_bias && n < sq.sk) {
             const T* bcol = reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
                             (int64_t)h * p.bias.s[1] + (int64_t)n * p.bias.s[3];
 #pragma unroll

@@ -362,7 +362,12 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         } else {
 #pragma unroll
           for (int c = 0; c < 32; ++c) pr[c] *= p.qk_scale;
-          if (p.has_bias && n < sq.sk) {
+          if (p.has_bias && p.bias_vec && mbase + 32 <= sq.sq && r0 + quarter * 32 + 32 <= sq.sk) {
+            // the warp's whole 32 x 32 bias tile is inside the sequence: vector loads and a transpose
+            add_bias_column32<T>(pr, reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
+                                         (int64_t)h * p.bias.s[1] + (int64_t)mbase * p.bias.s[2] + (r0 + quarter * 32),
+                                 p.bias.s[2], lane);
+          } else if (p.has_bias && n < sq.sk) {
             const T* bcol = reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
                             (int64_t)h * p.bias.s[1] + (int64_t)n * p.bias.s[3];
 #pragma unroll
