@@ -57,6 +57,15 @@ CONFIGS = {
                 Hq=16, Hk=16, S=2048, D=72, causal=(0, 0, 0), p=0.2, bias=True),
 }
 
+# Profiling aids, reachable through --only-config only (they isolate one cost of the configurations
+# above; no bench line is made from them).
+PROFILE_CONFIGS = {
+    "dropout_d128": dict(desc="dropout 0.1 bf16 B=4 H=16 S=2048 D=128", dtype="bf16", B=4, Hq=16, Hk=16, S=2048, D=128,
+                         causal=(0, 0, 0), p=0.1),
+    "plain_d256": dict(desc="dense fp16 B=8 H=16 S=2048 D=256", dtype="fp16", B=8, Hq=16, Hk=16, S=2048, D=256,
+                       causal=(0, 0, 0)),
+}
+
 # dram__bytes_read.sum + dram__bytes_write.sum per launch (bytes) of the C2 kernels, from the ncu
 # capture at batch 2 summarised in profiles/tcgen05_kernels_dense_causal_bf16_B2_H32_S4096_D128.md;
 # per-(batch, head) work is independent, so a launch at batch B moves B/2 times as much.
@@ -183,7 +192,7 @@ class Problem:
         import numpy as np
         import torch
         from aotriton_b200 import cabi
-        c = dict(CONFIGS[name])
+        c = dict(CONFIGS[name] if name in CONFIGS else PROFILE_CONFIGS[name])
         if batch is not None:
             c["B"] = batch
         self.name, self.c, self.cabi = name, c, cabi
@@ -381,7 +390,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="all", choices=["all", "none"] + sorted(CONFIGS),
                     help="which configurations the `configs` block measures beside the C2 headline (1 GPU)")
-    ap.add_argument("--only-config", default=None, choices=sorted(CONFIGS),
+    ap.add_argument("--only-config", default=None, choices=sorted(CONFIGS) + sorted(PROFILE_CONFIGS),
                     help="run just this configuration's forward and backward three times and print their times "
                          "(a short, exactly known launch sequence for profiler captures); no headline")
     ap.add_argument("--config-batch", type=int, default=None,

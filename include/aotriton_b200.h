@@ -244,7 +244,8 @@ AB200_API int ab200_stream_check(void* stream);
  * For the calling thread's following launches: `wait_limit_kcycles` bounds every in-kernel
  * wait (units of 1024 SM cycles, 0 = the default of about a second) and `drop_copy` makes
  * the producer leave out one tile copy (1 = the forward's first V block, 2 = the dK/dV
- * kernel's first Q/dO block, 3 = the dQ kernel's first V block, 0 = none), so that a wait
+ * kernel's first Q/dO block, 3 = the dQ kernel's first V block, 0 = none; for head dims above
+ * 128: 2 = the first block's Q of the dV and dO of the dK kernel, 3 = its V), so that a wait
  * runs out, the kernel records which one and returns normally.  Nothing faults or hangs:
  * the kernel takes a few limits to drain.  Call with (0, 0) to restore normal operation. */
 AB200_API void ab200_debug_bounded_wait_test(int drop_copy, unsigned int wait_limit_kcycles);
