@@ -389,10 +389,9 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     const uint64_t k_km = kmajor_base(smem_u32(smem + L::kResA)), v_km = kmajor_base(smem_u32(smem + L::kResB));
     const uint64_t q_km = kmajor_base(smem_u32(smem + L::kRingA)), do_km = kmajor_base(smem_u32(smem + L::kRingB));
     const uint64_t q_mn = mnmajor_base(smem_u32(smem + L::kRingA)), do_mn = mnmajor_base(smem_u32(smem + L::kRingB));
-    // fused form: K as the M-major A operand of dQ^T, the dS^T tile as its N-major B operand and as
-    // the K-major A operand of dK
+    // fused form: K as the M-major A operand of dQ^T, the dS^T tile as its N-major B operand
     const uint64_t k_mn = mnmajor_base(smem_u32(smem + L::kResA));
-    const uint64_t ds_mn = mnmajor_base(smem_u32(smem + L::kStage)), ds_km = kmajor_base(smem_u32(smem + L::kStage));
+    const uint64_t ds_mn = mnmajor_base(smem_u32(smem + L::kStage));
     constexpr uint32_t kIdescDQT = instr_desc_f16(Fmt<T>::code, 128, 128, 1, 1);
     auto wait = [&](int bar, uint32_t parity, uint32_t where) {
       return __all_sync(0xffffffffu, mbar_wait(&bars[bar], parity, abort_flag, status, where)) != 0;
@@ -466,17 +465,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-#if !defined(AB200_FUSED_KMAJOR_TEST)
             mma_ss(tmem_base + kColS, k_mn + mnmajor_step(kk), ds_mn + mnmajor_step(kk), kIdescDQT, kk > 0 ? 1u : 0u);
-#elif AB200_FUSED_KMAJOR_TEST == 1   // timing experiments only (wrong results): both operands K-major
-            mma_ss(tmem_base + kColS, k_km + kmajor_step(kk), ds_km + kmajor_step(kk), kIdescSS, kk > 0 ? 1u : 0u);
-#elif AB200_FUSED_KMAJOR_TEST == 2   // A K-major, B N-major
-            mma_ss(tmem_base + kColS, k_km + kmajor_step(kk), ds_mn + mnmajor_step(kk),
-                   instr_desc_f16(Fmt<T>::code, 128, 128, 0, 1), kk > 0 ? 1u : 0u);
-#else                                // A M-major, B K-major
-            mma_ss(tmem_base + kColS, k_mn + mnmajor_step(kk), ds_km + kmajor_step(kk),
-                   instr_desc_f16(Fmt<T>::code, 128, 128, 1, 0), kk > 0 ? 1u : 0u);
-#endif
           mma_commit(&bars[L::bDqFull]);
         }
         __syncwarp();
@@ -653,11 +642,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int c = 8 * c8 + j;
-#ifndef AB200_FUSED_NO_RED
             if (c < dq_rows) atomicAdd(dq_dst + (int64_t)c * p.dqk, v[j]);
-#else
-            if (c < dq_rows && v[j] == 123456.f) dq_dst[(int64_t)c * p.dqk] = 0.f;
-#endif
           }
         }
       };
