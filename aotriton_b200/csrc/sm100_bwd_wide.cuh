@@ -13,10 +13,10 @@
 //   dK     K, V                  dO (early), Q (late)    S' = K Q_i^T, dP' = V dO_i^T; dK += dS' Q_i
 //   dQ     Q, dO                 V (early), K (late)     S' = Q K_i^T, dP' = dO V_i^T; dQ += dS' K_i
 //
-// "early" tiles feed only the first GEMMs of a block and live in one stage; "late" tiles also feed the
-// accumulating GEMM at the block's end and live in two stages, so the S' / dP' GEMMs of block i+1
-// run while the compute warps work on block i.  Shared memory: 2 x 64 KB resident, 2 x 32 KB late,
-// 32 KB early.  Tensor memory: [0,64) S', [64,128) and [128,192) two dP' buffers, whose first columns
+// "early" tiles feed only the first GEMMs of a block and live in one stage (two for dV, in the place
+// of the second resident tile); "late" tiles also feed the accumulating GEMM at the block's end and
+// live in two stages, so the dP' / S' GEMMs of block i+1 run while the compute warps work on block i.
+// Shared memory: 2 x 64 KB resident, 2 x 32 KB late, 32 KB early.  Tensor memory: [0,64) S', [64,128) and [128,192) two dP' buffers, whose first columns
 // then take the packed 16-bit P' / dS' (the A operand of the accumulating GEMM), [256,512) the
 // accumulator.  Twelve warps: TMA producer, MMA issuer, logsumexp/delta stager (dV, dK), one idle,
 // eight compute warps (thread = one row of the 128 x 64 score tile, two warpgroups split its columns
@@ -40,8 +40,8 @@ struct WideSmem {
   static constexpr int kAux = kEarly + kStr;             // 2 stages x (64 lse2 + 64 delta) floats
   static constexpr int kAuxFlag = kAux + 2 * 2 * kNB * 4;
   static constexpr int kBars = kAuxFlag + 16;
-  static constexpr int bResFull = 0, bLateFull = 1, bLateEmpty = 3, bEarlyFull = 5, bEarlyEmpty = 6, bSFull = 7,
-                       bSRead = 8, bDpFull = 9, bDsFull = 11, bAccDone = 13, bAuxFull = 14, bAuxEmpty = 16, bCount = 18;
+  static constexpr int bResFull = 0, bLateFull = 1, bLateEmpty = 3, bEarlyFull = 5, bEarlyEmpty = 7, bSFull = 9,
+                       bSRead = 10, bDpFull = 11, bDsFull = 13, bAccDone = 15, bAuxFull = 16, bAuxEmpty = 18, bCount = 20;
   static constexpr int kTmemSlot = kBars + bCount * 8;
   static constexpr int kAbort = kTmemSlot + 8;
   static constexpr int kUsed = kAbort + 8;
@@ -70,6 +70,10 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
   using L = WideSmem;
   constexpr bool kKeys = MODE != kWideDQ;      // the CTA's rows are keys
   constexpr bool kHasDp = MODE != kWideDV;
+  // The early tile has one stage; dV, which keeps only K resident, gives it two in the second
+  // resident tile's place.
+  constexpr int kEarlyStages = MODE == kWideDV ? 2 : 1;
+  constexpr int kEarlyBase = MODE == kWideDV ? WideSmem::kResB : WideSmem::kEarly;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
@@ -118,8 +122,10 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       mbar_init(&bars[L::bAuxFull + s], 1);
       mbar_init(&bars[L::bAuxEmpty + s], kWideCompute);
     }
-    mbar_init(&bars[L::bEarlyFull], 1);
-    mbar_init(&bars[L::bEarlyEmpty], 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars[L::bEarlyFull + s], 1);
+      mbar_init(&bars[L::bEarlyEmpty + s], 1);
+    }
     mbar_init(&bars[L::bSFull], 1);
     mbar_init(&bars[L::bSRead], kWideCompute);
     mbar_init(&bars[L::bAccDone], 1);
@@ -153,25 +159,30 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         const int hs = kKeys ? hk * p.group + hg : hk;
         const int srow = (int)(col_tok0 + (int64_t)(cb_lo + cb) * kNB);
         if (++cb == ncb) { cb = 0; ++hg; }
+        // the early tile first: it is what the block's first GEMM waits for
+        const int es = i % kEarlyStages;
+        if (!mbar_wait(&bars[L::bEarlyEmpty + es], ((uint32_t)(i / kEarlyStages) & 1u) ^ 1u, abort_flag, status, 0x3100)) break;
+        if (!(drop_first && i == 0)) {
+          mbar_expect_tx(&bars[L::bEarlyFull + es], L::kStr);
+          for (int b = 0; b < L::kBoxes; ++b)
+            tma_load_4d(smem + kEarlyBase + es * L::kStr + b * L::kStrBox, &tm_early, &bars[L::bEarlyFull + es], b * 64, srow,
+                        hs, sq.bidx);
+          issued_e = i + 1;
+        }
         if (!mbar_wait(&bars[L::bLateEmpty + s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag, status, 0x3000)) break;
         mbar_expect_tx(&bars[L::bLateFull + s], L::kStr);
         for (int b = 0; b < L::kBoxes; ++b)
           tma_load_4d(smem + L::kLate + s * L::kStr + b * L::kStrBox, &tm_late, &bars[L::bLateFull + s], b * 64, srow, hs,
                       sq.bidx);
         issued_l = i + 1;
-        if (!mbar_wait(&bars[L::bEarlyEmpty], ((uint32_t)i & 1u) ^ 1u, abort_flag, status, 0x3100)) break;
-        if (drop_first && i == 0) continue;
-        mbar_expect_tx(&bars[L::bEarlyFull], L::kStr);
-        for (int b = 0; b < L::kBoxes; ++b)
-          tma_load_4d(smem + L::kEarly + b * L::kStrBox, &tm_early, &bars[L::bEarlyFull], b * 64, srow, hs, sq.bidx);
-        issued_e = i + 1;
       }
       if (*abort_flag) {
         // Let copies that are still in flight land before the CTA gives its shared memory back.
         mbar_wait_quiet(&bars[L::bResFull], 0, abort_flag);
         for (int i = max(0, issued_l - 2); i < issued_l; ++i)
           mbar_wait_quiet(&bars[L::bLateFull + (i & 1)], (uint32_t)(i >> 1) & 1u, abort_flag);
-        if (issued_e > 0) mbar_wait_quiet(&bars[L::bEarlyFull], (uint32_t)(issued_e - 1) & 1u, abort_flag);
+        for (int i = max(drop_first ? 1 : 0, issued_e - kEarlyStages); i < issued_e; ++i)
+          mbar_wait_quiet(&bars[L::bEarlyFull + i % kEarlyStages], (uint32_t)(i / kEarlyStages) & 1u, abort_flag);
       }
     }
     __syncwarp();
@@ -186,7 +197,7 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     const uint64_t r2_km = smem_desc_sw128(smem_u32(smem + L::kResB), 16, 1024);
     const uint64_t late_km = smem_desc_sw128(smem_u32(smem + L::kLate), 16, 1024);
     const uint64_t late_mn = smem_desc_sw128(smem_u32(smem + L::kLate), L::kStrBox, 1024);
-    const uint64_t early_km = smem_desc_sw128(smem_u32(smem + L::kEarly), 16, 1024);
+    const uint64_t early_km = smem_desc_sw128(smem_u32(smem + kEarlyBase), 16, 1024);
     constexpr uint32_t kStageStep = L::kStr >> 4;
     // k-step kk of a K-major tile: head-dim columns 16kk..16kk+15 (box kk / 4, 32 bytes per step inside it)
     auto res_step = [](int kk) { return (uint32_t)(kk >> 2) * (uint32_t)(L::kResBox >> 4) + (uint32_t)(kk & 3) * 2u; };
@@ -197,26 +208,45 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     // rows of streamed block i that belong to the sequence (a partial last block holds a neighbour's
     // tokens or padding beyond them, which must not reach a product: they are zeroed in place)
     auto valid_rows = [&](int i) { return cols_total - (cb_lo + (kKeys ? i % ncb : i)) * kNB; };
-    // the GEMMs that only need the block's tiles: S'_i, and dP'_i into dP buffer i & 1
+    // the GEMMs that only need the block's tiles: dP'_i into dP buffer i & 1, then S'_i into the one S'
+    // buffer once the compute warps have copied S'_{i-1} out.  (dP' goes first: the late tile S' reads
+    // was requested only when the accumulating GEMM of block i-2 had finished, and dP' gives that copy
+    // time to land.)
     auto issue_early = [&](int i) -> bool {
       const uint32_t s = (uint32_t)i & 1u;
+      const uint32_t es = (uint32_t)(i % kEarlyStages), epar = (uint32_t)(i / kEarlyStages) & 1u;
       if constexpr (MODE == kWideDV) {
-        if (!wait(L::bEarlyFull, s, 0x3200)) return false;
+        if (i > 0 && !wait(L::bSRead, (uint32_t)(i - 1) & 1u, 0x3800)) return false;
+        if (!wait(L::bEarlyFull + es, epar, 0x3200)) return false;
         tc_fence_after();
+        const uint64_t ea = early_km + (uint64_t)(es * kStageStep);
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 16; ++kk)
-            if (kk < ksteps_qk)
-              mma_ss(tmem_base + kWColS, r1_km + res_step(kk), early_km + str_step(kk), kIdescS, kk > 0 ? 1u : 0u);
+            if (kk < ksteps_qk) mma_ss(tmem_base + kWColS, r1_km + res_step(kk), ea + str_step(kk), kIdescS, kk > 0 ? 1u : 0u);
           mma_commit(&bars[L::bSFull]);
-          mma_commit(&bars[L::bEarlyEmpty]);
+          mma_commit(&bars[L::bEarlyEmpty + es]);
           // the accumulating GEMM of block i-2 has run: its P' buffer can be written again
           mma_commit(&bars[L::bDpFull + s]);
         }
         __syncwarp();
       } else {
-        if (!wait(L::bLateFull + s, (uint32_t)(i >> 1) & 1u, 0x3300)) return false;
         const int valid = valid_rows(i);
+        if (!wait(L::bEarlyFull + es, epar, 0x3400)) return false;
+        if (valid < kNB) zero_tail_rows_streamed(smem + kEarlyBase + es * L::kStr, valid, lane);
+        tc_fence_after();
+        const uint64_t ea = early_km + (uint64_t)(es * kStageStep);
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 16; ++kk)
+            if (kk < ksteps_vo)
+              mma_ss(tmem_base + kWColDP + s * 64u, r2_km + res_step(kk), ea + str_step(kk), kIdescS, kk > 0 ? 1u : 0u);
+          mma_commit(&bars[L::bDpFull + s]);
+          mma_commit(&bars[L::bEarlyEmpty + es]);
+        }
+        __syncwarp();
+        if (i > 0 && !wait(L::bSRead, (uint32_t)(i - 1) & 1u, 0x3800)) return false;
+        if (!wait(L::bLateFull + s, (uint32_t)(i >> 1) & 1u, 0x3300)) return false;
         if (valid < kNB) zero_tail_rows_streamed(smem + L::kLate + s * L::kStr, valid, lane);
         tc_fence_after();
         const uint64_t la = late_km + (uint64_t)(s * kStageStep);
@@ -225,18 +255,6 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           for (int kk = 0; kk < 16; ++kk)
             if (kk < ksteps_qk) mma_ss(tmem_base + kWColS, r1_km + res_step(kk), la + str_step(kk), kIdescS, kk > 0 ? 1u : 0u);
           mma_commit(&bars[L::bSFull]);
-        }
-        __syncwarp();
-        if (!wait(L::bEarlyFull, s, 0x3400)) return false;
-        if (valid < kNB) zero_tail_rows_streamed(smem + L::kEarly, valid, lane);
-        tc_fence_after();
-        if (elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < 16; ++kk)
-            if (kk < ksteps_vo)
-              mma_ss(tmem_base + kWColDP + s * 64u, r2_km + res_step(kk), early_km + str_step(kk), kIdescS, kk > 0 ? 1u : 0u);
-          mma_commit(&bars[L::bDpFull + s]);
-          mma_commit(&bars[L::bEarlyEmpty]);
         }
         __syncwarp();
       }
@@ -265,15 +283,12 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       __syncwarp();
       return true;
     };
-    // order on the tensor pipe:  S'_{i+1} dP'_{i+1} | acc_i   (S' has one buffer: S'_{i+1} follows the
+    // order on the tensor pipe:  dP'_{i+1} S'_{i+1} | acc_i   (S' has one buffer: S'_{i+1} follows the
     // compute warps' copy of S'_i into registers; dP'_{i+1} takes the buffer acc_{i-1} has read)
     bool ok = wait(L::bResFull, 0, 0x3700);
     if (ok) ok = issue_early(0);
     for (int i = 0; ok && i < niter; ++i) {
-      if (i + 1 < niter) {
-        ok = wait(L::bSRead, (uint32_t)i & 1u, 0x3800) && issue_early(i + 1);
-        if (!ok) break;
-      }
+      if (i + 1 < niter && !(ok = issue_early(i + 1))) break;
       ok = issue_acc(i);
     }
   } else if (warp == 2) {
