@@ -192,6 +192,26 @@ template <> __device__ __forceinline__ float from_f32<float>(float x) { return x
 template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
+// dBias of query rows [m0, m0 + rows) outside the key columns [c_lo, c_hi) that the calling CTA's
+// block loop visits.  A causal or windowed problem skips whole key blocks; the gradient of the bias
+// there is zero, and it is written, so that dBias is defined everywhere inside the sequence.  (The
+// reference leaves those entries as they were: modules/flash/kernel/bwd_inner_dq.py:200-204 stores
+// dB only in the blocks its loop visits.)  Called by all threads of the CTA.
+template <typename T>
+__device__ __forceinline__ void zero_dbias_outside(const Params& p, const Seq& sq, int h, int m0, int rows, int c_lo,
+                                                   int c_hi) {
+  if (!p.has_dbias || !p.causal) return;
+  const int lane = threadIdx.x & 31, nwarps = (int)blockDim.x >> 5;
+  for (int r = (int)threadIdx.x >> 5; r < rows; r += nwarps) {
+    const int m = m0 + r;
+    if (m >= sq.sq) break;
+    T* rowp = reinterpret_cast<T*>(p.dbias.ptr) + (int64_t)sq.bidx * p.dbias.s[0] + (int64_t)h * p.dbias.s[1] +
+              (int64_t)m * p.dbias.s[2];
+    for (int n = lane; n < min(c_lo, sq.sk); n += 32) rowp[(int64_t)n * p.dbias.s[3]] = from_f32<T>(0.f);
+    for (int n = max(c_hi, 0) + lane; n < sq.sk; n += 32) rowp[(int64_t)n * p.dbias.s[3]] = from_f32<T>(0.f);
+  }
+}
+
 // Round through the storage type, the way the reference casts P and dS before its GEMMs.
 template <typename T> __device__ __forceinline__ float round_to(float x) { return to_f32<T>(from_f32<T>(x)); }
 

@@ -327,6 +327,8 @@ __global__ void __launch_bounds__(kThreads) general_bwd_dq_kernel(const __grid_c
 
   int n_lo, n_hi;
   key_range(p, sq, m0, min(m0 + kTile, sq.sq) - 1, n_lo, n_hi);
+  if (n_hi >= n_lo) zero_dbias_outside<T>(p, sq, h, m0, kTile, (n_lo / kTile) * kTile, (n_hi / kTile + 1) * kTile);
+  else zero_dbias_outside<T>(p, sq, h, m0, kTile, 0, 0);
   const int m = m0 + r;
   for (int nb = n_lo / kTile; nb * kTile <= n_hi; ++nb) {
     const int n0 = nb * kTile;

@@ -974,10 +974,12 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
   key_range(p, sq, m0, min(m0 + kBlk, sq.sq) - 1, n_lo, n_hi);
   if (n_hi < n_lo) {
     zero_rows<T>(p.dq, sq.bidx, h, sq.q0, m0, sq.sq, p.dqk);
+    zero_dbias_outside<T>(p, sq, h, m0, kBlk, 0, 0);
     return;
   }
   const int jb_lo = n_lo / kBlk;
   const int niter = n_hi / kBlk - jb_lo + 1;
+  zero_dbias_outside<T>(p, sq, h, m0, kBlk, jb_lo * kBlk, (jb_lo + niter) * kBlk);
 
   if (threadIdx.x == 0) {
     init_abort_and_limit(abort_flag, p.wait_limit_kcycles);

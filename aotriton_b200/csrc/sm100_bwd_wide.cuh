@@ -104,10 +104,12 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
   const int64_t row_tok0 = kKeys ? sq.k0 : sq.q0, col_tok0 = kKeys ? sq.q0 : sq.k0;
   if (c_hi < c_lo) {      // rows nothing attends to / that attend to nothing: the gradient is zero
     zero_rows<T>(outv, sq.bidx, hrow, row_tok0, r0, rows_total, d_out);
+    if constexpr (MODE == kWideDQ) zero_dbias_outside<T>(p, sq, hrow, r0, kBlk, 0, 0);
     return;
   }
   const int cb_lo = c_lo / kNB;
   const int ncb = c_hi / kNB - cb_lo + 1;
+  if constexpr (MODE == kWideDQ) zero_dbias_outside<T>(p, sq, hrow, r0, kBlk, cb_lo * kNB, (cb_lo + ncb) * kNB);
   const int niter = kKeys ? ncb * p.group : ncb;      // dV / dK walk the q heads of the kv head's group
   const int hk = kKeys ? hrow : hrow / p.group;
 
