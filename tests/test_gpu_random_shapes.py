@@ -40,14 +40,15 @@ def _draw(seed: int):
         causal = (3, r.randint(0, 300), r.randint(0, 300))
     p = r.choice([0.0, 0.0, 0.3])
     bias = r.random() < 0.3
-    return dt, B, Hk * G, Hk, Sq, Sk, D, Dv, causal, p, bias
+    bshd = r.random() < 0.3      # (B, S, H, D) storage behind the logical (B, H, S, D) views
+    return dt, B, Hk * G, Hk, Sq, Sk, D, Dv, causal, p, bias, bshd
 
 
-@pytest.mark.parametrize("family", ["auto", "general"])
+@pytest.mark.parametrize("family", ["auto", "general", "fused"])
 @pytest.mark.parametrize("seed", range(96))
 def test_random_shape_vs_oracle(seed, family):
     from _gpu_runner import run_fwd_bwd
-    dt, B, Hq, Hk, Sq, Sk, D, Dv, (ct, wl, wr), p, use_bias = _draw(seed)
+    dt, B, Hq, Hk, Sq, Sk, D, Dv, (ct, wl, wr), p, use_bias, bshd = _draw(seed)
     q, k, v, do = randn_inputs((B, Hq, Sq, D), (B, Hk, Sk, D), (B, Hk, Sk, Dv), dt, seed=1000 + seed)
     bias = None
     if use_bias:
@@ -60,10 +61,12 @@ def test_random_shape_vs_oracle(seed, family):
     keep = A.keep_masks(sd, off1 + off2, B, Hq, Sq, Sk, p) if p > 0 else None
     ref = A.attention(q, k, v, sm_scale=sm, bias=bias, mask=mask, keep=keep, dropout_p=p, dout=do)
     res = run_fwd_bwd(q, k, v, do, sm_scale=sm, bias=bias, causal_type=ct, window_left=wl, window_right=wr,
-                      dropout_p=p, seed=sd, offset1=off1, offset2=off2, family=family, want_dbias=use_bias)
-    tag = f"seed {seed}/{family}: {dt} B{B} H{Hq}:{Hk} S{Sq}x{Sk} D{D}x{Dv} causal{(ct, wl, wr)} p{p} bias{use_bias}"
+                      dropout_p=p, seed=sd, offset1=off1, offset2=off2, family=family, want_dbias=use_bias,
+                      keep_layout=(lambda t: t.transpose(1, 2).contiguous().transpose(1, 2)) if bshd else None)
+    tag = (f"seed {seed}/{family}: {dt} B{B} H{Hq}:{Hk} S{Sq}x{Sk} D{D}x{Dv} causal{(ct, wl, wr)} p{p} bias{use_bias} "
+           f"bshd{bshd}")
     for which in ("fwd", "bwd"):
-        want = 1 if family == "general" else expected_family(dt, D, Dv, which, False, use_bias)
+        want = 1 if family == "general" else expected_family(dt, D, Dv, which, family == "fused", use_bias)
         assert res[which + "_family"] == want, f"{tag}: {which} ran on family {res[which + '_family']}, expected {want}"
     for key in ("out", "dq", "dk", "dv"):
         ok, err = close(res[key].float(), getattr(ref, key), ATOL[dt])
