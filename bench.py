@@ -285,6 +285,32 @@ class Timer:
         return dict(median_ms=statistics.median(ms), min_ms=ms[0], reps=reps)
 
 
+def bind_to_gpu_numa_node(local):
+    """Best effort: run this process (and so first-touch its pinned host buffers) on the CPUs of the NUMA
+    node the GPU hangs off, so that the host <-> device copies of different ranks do not all cross one
+    socket's memory.  Returns what it did, for the e2e record; the caller restores the affinity once the
+    buffers exist."""
+    import torch
+    try:
+        pr = torch.cuda.get_device_properties(local)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        base = Path("/sys/bus/pci/devices") / bdf
+        node = int((base / "numa_node").read_text().strip())
+        cpus = (base / "local_cpulist").read_text().strip()
+        want = set()
+        for part in cpus.split(","):
+            lo, _, hi = part.partition("-")
+            want.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        use = want & allowed
+        if node < 0 or not use:
+            return dict(numa_node=node, bound=False, why="no local CPUs among the allowed ones")
+        os.sched_setaffinity(0, use)
+        return dict(numa_node=node, bound=True, cpus=len(use), restore=allowed)
+    except Exception as e:       # sysfs absent, attributes missing, not permitted ...
+        return dict(bound=False, why=f"{type(e).__name__}: {e}"[:120])
+
+
 def tfl(flops, ms):
     return flops / (ms * 1e-3) / 1e12
 
@@ -435,6 +461,7 @@ def main():
     B, H, S, D = args.batch, c2["Hq"], c2["S"], c2["D"]
     warm = max(args.warmup, 3)
     dev = torch.device("cuda", local)
+    numa = bind_to_gpu_numa_node(local)
     g = torch.Generator().manual_seed(1234 + rank)
     host = [torch.randn(B, H, S, D, generator=g, dtype=torch.float32).to(torch.bfloat16).pin_memory()
             for _ in range(4)]
@@ -443,6 +470,8 @@ def main():
     lse = torch.empty(B * H, S, dtype=torch.float32, device=dev)
     delta = torch.empty_like(lse)
     host_out = [torch.empty(B, H, S, D, dtype=torch.bfloat16).pin_memory() for _ in range(4)]
+    if numa.get("bound"):
+        os.sched_setaffinity(0, numa.pop("restore"))
     null64 = torch.empty(0, dtype=torch.uint64, device=dev)
     atomic = torch.zeros(1, dtype=torch.int32, device=dev)
     sm = D ** -0.5
@@ -626,7 +655,7 @@ def main():
         line["e2e"] = dict(value=world * tfl(ffwd + fbwd, ms_e2e), unit="TFLOPS", ms_per_step=ms_e2e,
                            h2d_bytes_per_step=4 * nbytes, d2h_bytes_per_step=4 * nbytes,
                            h2d_gbs_per_rank=4 * nbytes / (ms_e2e * 1e-3) / 1e9,
-                           d2h_gbs_per_rank=4 * nbytes / (ms_e2e * 1e-3) / 1e9,
+                           d2h_gbs_per_rank=4 * nbytes / (ms_e2e * 1e-3) / 1e9, host_numa=numa,
                            bound="host <-> device copies: 0.5 GiB each way per step per rank over the box's PCIe "
                                  "and host memory, shared by all ranks; the kernels take ms_per_step of the headline",
                            how="pinned host buffers; copies in, compute and copies out of consecutive steps overlap "
