@@ -99,6 +99,31 @@ def test_launch_counts_and_variants(fake):
     assert L.ab200_attn_bwd(C.byref(a), None) == 0 and L.ab200_last_bwd_family() == 2
 
 
+def test_wide_heads_launch_one_kernel_per_gradient(fake):
+    """Head dims above 128: forward on its 256-wide instantiation, backward as preprocess + dV + dK + dQ;
+    no fused form; a launch failure in the middle stops the call there."""
+    L = fake
+    n0 = L.ab200_launch_count()
+    assert L.ab200_attn_fwd(C.byref(_fwd_args(D=256)), None) == 0
+    assert L.ab200_launch_count() - n0 == 1 and L.ab200_last_fwd_family() == 2
+    n0, e0 = L.ab200_launch_count(), L.ab200_debug_host_call_count(CALLS["encode"])
+    assert L.ab200_attn_bwd(C.byref(_bwd_args(D=192)), None) == 0
+    assert L.ab200_launch_count() - n0 == 4 and L.ab200_last_bwd_family() == 2
+    assert L.ab200_debug_host_call_count(CALLS["encode"]) - e0 == 8     # four tile maps for dV + dK, four for dQ
+    a = _bwd_args(D=256)
+    a.dq_acc = 0x60000000
+    L.ab200_set_kernel_family(3)
+    assert L.ab200_bwd_uses_dq_acc(C.byref(a), None) == 0
+    n0 = L.ab200_launch_count()
+    assert L.ab200_attn_bwd(C.byref(a), None) == 0
+    assert L.ab200_launch_count() - n0 == 4 and L.ab200_last_bwd_family() == 2
+    L.ab200_set_kernel_family(0)
+    L.ab200_debug_host_calls(1, CALLS["launch"], 719, 2)      # the third launch (dK) fails
+    n0 = L.ab200_launch_count()
+    assert L.ab200_attn_bwd(C.byref(_bwd_args(D=256)), None) == 719
+    assert L.ab200_launch_count() - n0 == 2
+
+
 @pytest.mark.parametrize("call,code", [("func_attr", 1), ("symbol", 13), ("encode", 1), ("launch", 719),
                                        ("device_attr", 101)])
 def test_injected_failures_come_back_and_stop_the_call(fake, call, code):
