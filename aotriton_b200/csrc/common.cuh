@@ -181,6 +181,37 @@ __device__ __forceinline__ uint32_t dropout_keep4(const DropoutCtx& d, int m, in
   return k;
 }
 
+// The same generator with its ten round keys precomputed (they depend on the seed only): a thread
+// that draws many counters saves the two key additions of every round.
+struct PhiloxKeys { uint32_t k0[10], k1[10]; };
+
+__device__ __forceinline__ PhiloxKeys philox_keys(uint64_t seed) {
+  PhiloxKeys r;
+  uint32_t a = (uint32_t)seed, b = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int i = 0; i < 10; ++i) { r.k0[i] = a; r.k1[i] = b; a += 0x9E3779B9u; b += 0xBB67AE85u; }
+  return r;
+}
+
+__device__ __forceinline__ uint32_t dropout_keep4_keys(const DropoutCtx& d, const PhiloxKeys& ks, int m, int c) {
+  const uint32_t kA = 0xD2511F53u, kB = 0xCD9E8D57u;
+  const uint64_t offset = d.base + (uint64_t)m * d.stride + (uint64_t)c;
+  uint32_t c0 = (uint32_t)offset, c1 = (uint32_t)(offset >> 32), c2 = 0u, c3 = 0u;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint64_t pa = (uint64_t)kA * c0, pb = (uint64_t)kB * c2;
+    const uint32_t n0 = (uint32_t)(pb >> 32) ^ c1 ^ ks.k0[i];
+    const uint32_t n2 = (uint32_t)(pa >> 32) ^ c3 ^ ks.k1[i];
+    c1 = (uint32_t)pb; c3 = (uint32_t)pa; c0 = n0; c2 = n2;
+  }
+  uint32_t k = 0;
+  k |= ((int32_t)c0 > d.threshold) ? 1u : 0u;
+  k |= ((int32_t)c2 > d.threshold) ? 2u : 0u;
+  k |= ((int32_t)c1 > d.threshold) ? 4u : 0u;
+  k |= ((int32_t)c3 > d.threshold) ? 8u : 0u;
+  return k;
+}
+
 // ---------------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f32(T x);
 template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }

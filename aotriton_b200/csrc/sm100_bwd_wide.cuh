@@ -344,6 +344,8 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     // the tightest bounds over the warp's rows: a block needs masking iff it is not inside them
     const int warp_lo = __reduce_max_sync(0xffffffffu, v_lo), warp_hi = __reduce_min_sync(0xffffffffu, v_hi);
     bool ok = true;
+    PhiloxKeys pkeys;      // Philox round keys: they depend on the seed only
+    if (p.dropout_on) pkeys = philox_keys(p.seed_ptr ? *p.seed_ptr : 0ull);
     if constexpr (kKeys) {
       const int n = row;
       for (int i = 0, hg = 0, cb = 0; i < niter; ++i) {
@@ -420,7 +422,7 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           uint32_t mine = 0u;
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            mine |= dropout_keep4(dctx, min(mbase + q4 + 4 * k, p.max_sq - 1), n >> 2) << (4 * k);
+            mine |= dropout_keep4_keys(dctx, pkeys, min(mbase + q4 + 4 * k, p.max_sq - 1), n >> 2) << (4 * k);
           keep = 0u;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -547,7 +549,7 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           keep = 0u;
           const int md = min(m, p.max_sq - 1);
 #pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4) keep |= dropout_keep4(dctx, md, (nbase >> 2) + c4) << (4 * c4);
+          for (int c4 = 0; c4 < 8; ++c4) keep |= dropout_keep4_keys(dctx, pkeys, md, (nbase >> 2) + c4) << (4 * c4);
         }
         const uint32_t a_col = tmem_base + lane_addr + kWColDP + (uint32_t)s * 64u + cbase;
         if (!mbar_wait(&bars[L::bDpFull + s], par2, abort_flag, status, 0x3D00)) { ok = false; break; }
