@@ -193,9 +193,8 @@ __device__ __forceinline__ PhiloxKeys philox_keys(uint64_t seed) {
   return r;
 }
 
-__device__ __forceinline__ uint32_t dropout_keep4_keys(const DropoutCtx& d, const PhiloxKeys& ks, int m, int c) {
+__device__ __forceinline__ Philox4 philox4x32_10_keys(const PhiloxKeys& ks, uint64_t offset) {
   const uint32_t kA = 0xD2511F53u, kB = 0xCD9E8D57u;
-  const uint64_t offset = d.base + (uint64_t)m * d.stride + (uint64_t)c;
   uint32_t c0 = (uint32_t)offset, c1 = (uint32_t)(offset >> 32), c2 = 0u, c3 = 0u;
 #pragma unroll
   for (int i = 0; i < 10; ++i) {
@@ -204,6 +203,23 @@ __device__ __forceinline__ uint32_t dropout_keep4_keys(const DropoutCtx& d, cons
     const uint32_t n2 = (uint32_t)(pa >> 32) ^ c3 ^ ks.k1[i];
     c1 = (uint32_t)pb; c3 = (uint32_t)pa; c0 = n0; c2 = n2;
   }
+  Philox4 r; r.w[0] = c0; r.w[1] = c1; r.w[2] = c2; r.w[3] = c3;
+  return r;
+}
+
+// Zero the dropped ones of the four scores v[0..3] = columns 4c..4c+3 of row m, straight from the
+// comparisons (no keep mask in between: for a consumer that applies the bits at once).
+__device__ __forceinline__ void dropout_zero4_keys(const DropoutCtx& d, const PhiloxKeys& ks, int m, int c, float* v) {
+  const Philox4 r = philox4x32_10_keys(ks, d.base + (uint64_t)m * d.stride + (uint64_t)c);
+  v[0] = ((int32_t)r.w[0] > d.threshold) ? v[0] : 0.f;
+  v[1] = ((int32_t)r.w[2] > d.threshold) ? v[1] : 0.f;
+  v[2] = ((int32_t)r.w[1] > d.threshold) ? v[2] : 0.f;
+  v[3] = ((int32_t)r.w[3] > d.threshold) ? v[3] : 0.f;
+}
+
+__device__ __forceinline__ uint32_t dropout_keep4_keys(const DropoutCtx& d, const PhiloxKeys& ks, int m, int c) {
+  const Philox4 r4 = philox4x32_10_keys(ks, d.base + (uint64_t)m * d.stride + (uint64_t)c);
+  const uint32_t c0 = r4.w[0], c1 = r4.w[1], c2 = r4.w[2], c3 = r4.w[3];
   uint32_t k = 0;
   k |= ((int32_t)c0 > d.threshold) ? 1u : 0u;
   k |= ((int32_t)c2 > d.threshold) ? 2u : 0u;

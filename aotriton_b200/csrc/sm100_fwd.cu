@@ -526,12 +526,7 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
         if (p.dropout_on) {
           const int mm = min(m, p.max_sq - 1);
 #pragma unroll
-          for (int c4 = half * 16; c4 < half * 16 + 16; ++c4) {
-            const uint32_t keep = dropout_keep4_keys(dctx, pkeys, mm, (n0 >> 2) + c4);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              if (!((keep >> i) & 1u)) sc[c4 * 4 + i] = 0.f;
-          }
+          for (int c4 = half * 16; c4 < half * 16 + 16; ++c4) dropout_zero4_keys(dctx, pkeys, mm, (n0 >> 2) + c4, &sc[c4 * 4]);
         }
         // P over the first 64 columns of this S buffer, two 16-bit values per column.
         {
