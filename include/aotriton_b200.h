@@ -109,7 +109,10 @@ typedef struct ab200_attn_fwd_args {
 typedef struct ab200_attn_bwd_args {
   ab200_attn_problem prob;
   ab200_view4 q, k, v, bias, out, dout;
-  ab200_view4 dq, dk, dv, dbias;    /* dbias absent or all-zero strides -> not written */
+  ab200_view4 dq, dk, dv, dbias;    /* dbias absent or all-zero strides -> not written; otherwise every entry inside
+                                     * the sequences is written, zero where a causal or windowed problem masks it (the
+                                     * reference stores dB only in the key blocks its loop visits,
+                                     * modules/flash/kernel/bwd_inner_dq.py:200-204) */
   const float* lse;                 /* as written by the forward */
   float* delta;                     /* scratch, same shape as lse (the "D" lazy tensor) */
   int32_t deterministic;            /* attn_options::deterministic: non-zero forbids the fused form below */
