@@ -603,10 +603,8 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     const int cbase = kWgCols * wg;
     uint32_t G = 0, live = 0, drawn = 0;
     bool ok = true;
-#ifndef AB200_NO_PHILOX_KEYS
     PhiloxKeys pkeys;      // Philox round keys: they depend on the seed only
     if (p.dropout_on) pkeys = philox_keys(p.seed_ptr ? *p.seed_ptr : 0ull);
-#endif
     for (int w = blockIdx.x; ok && w < nitems; w = next_item(drawn++, true)) {
       const DkdvItem it = dkdv_item(p, w);
       if (!it.valid) continue;
@@ -774,11 +772,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           uint32_t mine = 0u;            // nibble k: keep bits of keys 4a..4a+3 for query row mbase + q4 + 4k
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-#ifndef AB200_NO_PHILOX_KEYS
             mine |= dropout_keep4_keys(dctx, pkeys, min(mbase + q4 + 4 * k, p.max_sq - 1), n >> 2) << (4 * k);
-#else
-            mine |= dropout_keep4(dctx, min(mbase + q4 + 4 * k, p.max_sq - 1), n >> 2) << (4 * k);
-#endif
           keep = 0u;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -1196,10 +1190,8 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
     const bool simple = !p.has_bias && !__any_sync(0xffffffffu, fabsf(lse2) > 1.0e6f && lse2 != INFINITY);
     DropoutCtx dctx;
     if (p.dropout_on) dctx = dropout_ctx(p, z, h);
-#ifndef AB200_NO_PHILOX_KEYS
     PhiloxKeys pkeys;      // Philox round keys: they depend on the seed only
     if (p.dropout_on) pkeys = philox_keys(dctx.seed);
-#endif
     const int mm = min(m, sq.sq - 1);
     const T* bias_row = p.has_bias ? reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
                                          (int64_t)h * p.bias.s[1] + (int64_t)mm * p.bias.s[2]
@@ -1271,11 +1263,7 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
         keep = 0u;
         const int md = min(m, p.max_sq - 1);
 #pragma unroll
-#ifndef AB200_NO_PHILOX_KEYS
         for (int c4 = 0; c4 < 8; ++c4) keep |= dropout_keep4_keys(dctx, pkeys, md, (nbase >> 2) + c4) << (4 * c4);
-#else
-        for (int c4 = 0; c4 < 8; ++c4) keep |= dropout_keep4(dctx, md, (nbase >> 2) + c4) << (4 * c4);
-#endif
       }
       const uint32_t dp_col = tmem_base + lane_addr + kColDP + (uint32_t)(i & 1) * 128u + cbase;
       if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 7);
