@@ -113,3 +113,59 @@ def test_random_compact_varlen_vs_oracle(seed, family):
     for key in ("out", "dq", "dk", "dv"):
         ok, err = close(res[key].float(), getattr(ref, key), ATOL[dt])
         assert ok, f"{tag}: {key} max err {err}"
+
+
+@pytest.mark.parametrize("family", ["auto", "general"])
+@pytest.mark.parametrize("seed", range(16))
+def test_random_padded_and_strided_varlen_vs_oracle(seed, family):
+    """Padded varlen (rank-4 tensors, lengths from cu_seqlens) and strided varlen (THD storage with gaps,
+    offsets from seq_strides) with random lengths, head dims and windows; each sequence against the dense
+    oracle on its own slice."""
+    import numpy as np
+    from aotriton_b200 import cabi
+    from _gpu_runner import run_fwd_bwd
+    r = random.Random(9000 + seed)
+    dt = r.choice([torch.float16, torch.bfloat16])
+    Hk, G = r.choice([1, 2]), r.choice([1, 2])
+    Hq = Hk * G
+    D = 8 * r.randint(1, 32)
+    lens = [r.choice([1, 17, 63, 64, 65, 128, 129, 150, r.randint(1, 200)]) for _ in range(r.randint(2, 4))]
+    nseq, S = len(lens), max(lens)
+    cu = [0] + list(np.cumsum(lens))
+    ct, wl, wr = r.choice([(0, 0, 0), (3, TL, TL), (3, BR, BR), (3, r.randint(0, 150), r.randint(0, 150))])
+    sm = D ** -0.5
+    tag = f"seed {seed}/{family}: {dt} H{Hq}:{Hk} lens{lens} D{D} causal{(ct, wl, wr)}"
+
+    def check(got, ref, what, L):
+        for key in ("out", "dq", "dk", "dv"):
+            ok, err = close(got[key].float(), getattr(ref, key), ATOL[dt])
+            assert ok, f"{tag}: {what} {key} max err {err}"
+
+    # padded
+    q, k, v, do = randn_inputs((nseq, Hq, S, D), (nseq, Hk, S, D), (nseq, Hk, S, D), dt, seed=seed)
+    res = run_fwd_bwd(q, k, v, do, sm_scale=sm, causal_type=ct, window_left=wl, window_right=wr, cu_q=cu, cu_k=cu,
+                      max_sq=S, max_sk=S, family=family, varlen_type=cabi.VARLEN_PADDED)
+    for which in ("fwd", "bwd"):
+        want = 1 if family == "general" else expected_family(dt, D, D, which)
+        assert res[which + "_family"] == want, f"{tag}: padded {which} ran on family {res[which + '_family']}"
+    for z, L in enumerate(lens):
+        ref = A.attention(q[z:z + 1, :, :L], k[z:z + 1, :, :L], v[z:z + 1, :, :L], sm_scale=sm,
+                          mask=A.window_mask(L, L, ct, wl, wr), dout=do[z:z + 1, :, :L])
+        check({n: res[n][z:z + 1, :, :L] for n in ("out", "dq", "dk", "dv")}, ref, f"padded z={z}", L)
+    # strided: random gaps between the sequences
+    starts = [0]
+    for L in lens:
+        starts.append(starts[-1] + L + r.choice([0, 3, 16, 40]))
+    T = starts[-1]
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda H: torch.randn(1, T, H, D, generator=g).to(dt).transpose(1, 2)
+    q, k, v, do = mk(Hq), mk(Hk), mk(Hk), mk(Hq)
+    thd = lambda t: t.transpose(1, 2).contiguous().transpose(1, 2)
+    res = run_fwd_bwd(q, k, v, do, sm_scale=sm, causal_type=ct, window_left=wl, window_right=wr, cu_q=cu, cu_k=cu,
+                      max_sq=S, max_sk=S, family=family, varlen_type=cabi.VARLEN_STRIDED, seq_strides_q=starts,
+                      seq_strides_k=starts, keep_layout=thd)
+    for z, L in enumerate(lens):
+        a = starts[z]
+        ref = A.attention(q[:, :, a:a + L], k[:, :, a:a + L], v[:, :, a:a + L], sm_scale=sm,
+                          mask=A.window_mask(L, L, ct, wl, wr), dout=do[:, :, a:a + L])
+        check({n: res[n][:, :, a:a + L] for n in ("out", "dq", "dk", "dv")}, ref, f"strided z={z}", L)
