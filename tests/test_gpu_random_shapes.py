@@ -7,15 +7,19 @@ one-accumulator kernels for wider heads are hit), GQA groups, windows, dropout a
 that ragged last blocks, windows that miss whole blocks, single-block problems and dead rows meet every
 kernel.  Tolerances as in test_gpu_parity.py (atol = rtol = 2e-2 bf16, 1e-2 fp16; LSE 1e-3).
 """
+import os
 import random
 
 import pytest
 import torch
 
 from oracle import attention as A
-from _util import ATOL, LSE_ATOL, close, randn_inputs, expected_family
+from _util import ATOL, LSE_ATOL, FUDGE, close, randn_inputs, expected_family, reference_rule
 
 pytestmark = pytest.mark.gpu
+
+# AB200_SWEEP_FACTOR=N runs N times as many seeds (an occasional long sweep; the default keeps the suite short)
+SWEEP = max(1, int(os.environ.get("AB200_SWEEP_FACTOR", "1")))
 
 TL, BR = A.TOP_LEFT, A.BOTTOM_RIGHT
 
@@ -45,7 +49,7 @@ def _draw(seed: int):
 
 
 @pytest.mark.parametrize("family", ["auto", "general", "fused"])
-@pytest.mark.parametrize("seed", range(96))
+@pytest.mark.parametrize("seed", range(96 * SWEEP))
 def test_random_shape_vs_oracle(seed, family):
     from _gpu_runner import run_fwd_bwd
     dt, B, Hq, Hk, Sq, Sk, D, Dv, (ct, wl, wr), p, use_bias, bshd = _draw(seed)
@@ -68,18 +72,32 @@ def test_random_shape_vs_oracle(seed, family):
     for which in ("fwd", "bwd"):
         want = 1 if family == "general" else expected_family(dt, D, Dv, which, family == "fused", use_bias)
         assert res[which + "_family"] == want, f"{tag}: {which} ran on family {res[which + '_family']}, expected {want}"
+    lp = None
     for key in ("out", "dq", "dk", "dv"):
         ok, err = close(res[key].float(), getattr(ref, key), ATOL[dt])
+        if not ok and Sk > 1:
+            # Shapes with few keys and many queries (or the reverse) sum hundreds of 16-bit-rounded
+            # probabilities into one gradient element, which no flat tolerance fits; the reference suite's own
+            # criterion applies there: error relative to that of a math SDPA in the input dtype
+            # (modules/flash/tests/_common_test.py:460-495).
+            if lp is None:
+                lp = A.sdpa_math_reference(q, k, v, sm_scale=sm, bias=bias, mask=mask, keep=keep, dropout_p=p, dout=do,
+                                           acc_dtype=dt)
+            ok, err, tol = reference_rule(res[key].float(), getattr(ref, key), getattr(lp, key).float(), FUDGE[key])
+            assert ok, f"{tag}: {key} err {err} beyond the flat tolerance and the reference rule's {tol}"
         assert ok, f"{tag}: {key} max err {err}"
     ok, err = close(res["lse"].reshape(-1), ref.lse.reshape(-1).float(), LSE_ATOL)
     assert ok, f"{tag}: lse max err {err}"
     if use_bias:
-        ok, err = close(res["db"].float(), ref.db, ATOL[dt])
+        # dB = dS = P (dP - delta) per element, not a sum: it carries delta's error in full where P is near 1,
+        # and delta = rowsum(O dO) is taken from the 16-bit O (error ~ 2^-9 |O||dO| sqrt(D), which the other
+        # tests also allow for with 4 x the flat tolerance on delta)
+        ok, err = close(res["db"].float(), ref.db, ATOL[dt] * 4, ATOL[dt])
         assert ok, f"{tag}: db max err {err}"
 
 
 @pytest.mark.parametrize("family", ["auto", "general"])
-@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("seed", range(24 * SWEEP))
 def test_random_compact_varlen_vs_oracle(seed, family):
     """Token-packed sequences of random lengths (empty ones included) in THD storage."""
     import numpy as np
@@ -116,7 +134,7 @@ def test_random_compact_varlen_vs_oracle(seed, family):
 
 
 @pytest.mark.parametrize("family", ["auto", "general"])
-@pytest.mark.parametrize("seed", range(16))
+@pytest.mark.parametrize("seed", range(16 * SWEEP))
 def test_random_padded_and_strided_varlen_vs_oracle(seed, family):
     """Padded varlen (rank-4 tensors, lengths from cu_seqlens) and strided varlen (THD storage with gaps,
     offsets from seq_strides) with random lengths, head dims and windows; each sequence against the dense
