@@ -657,6 +657,11 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         const uint32_t lse2 = aux_s + (uint32_t)(s * 256 + cbase) * 4u;      // shared-space addresses
         const uint32_t dlt = lse2 + 128u * 4u;
         if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 4);
+        // (the warp's 32 x 32 bias tile, one 64-byte row per lane: on its way to L2 meanwhile)
+        if (p.has_bias && p.bias_vec)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
+                                                       (int64_t)h * p.bias.s[1] + (int64_t)min(mbase + lane, sq.sq - 1) * p.bias.s[2] +
+                                                       (it.n0 + quarter * 32)));
         // S^T of this block and its logsumexp/delta stage (two arrivals on one barrier)
         if (!mbar_wait(&bars[L::bSFull + s], (G >> 1) & 1u, abort_flag, status, 0x1800)) { ok = false; break; }
         if (threadIdx.x == AB200_TRACE_TID) AB200_STAMP(G, 0);
@@ -1204,6 +1209,8 @@ sm100_bwd_dq_kernel(const __grid_constant__ Params p, const __grid_constant__ CU
       const uint32_t par = (uint32_t)i & 1u;
       const int nbase = (jb_lo + i) * kBlk + cbase;     // first key of this thread's columns
       if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 4);
+      // (the thread's 64 bytes of bias for this block: on their way to L2 while the tensor pipe computes S)
+      if (p.has_bias && p.bias_vec) asm volatile("prefetch.global.L2 [%0];" ::"l"(bias_row + nbase));
       if (!mbar_wait(&bars[L::bSFull], par, abort_flag, status, 0x2600 + i)) { ok = false; break; }
       if (threadIdx.x == AB200_TRACE_TID) AB200_STAMPQ(i, 0);
       tc_fence_after();

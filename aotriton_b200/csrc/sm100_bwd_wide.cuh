@@ -356,6 +356,10 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         if (++cb == ncb) { cb = 0; ++hg; }
         const uint32_t lse2 = aux_s + (uint32_t)(s * 2 * kNB + cbase) * 4u;      // shared-space addresses
         const uint32_t dlt = lse2 + (uint32_t)kNB * 4u;
+        if (p.has_bias && p.bias_vec)      // the warp's 32 x 32 bias tile, one 64-byte row per lane, towards L2
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
+                                                       (int64_t)h * p.bias.s[1] + (int64_t)min(mbase + lane, sq.sq - 1) * p.bias.s[2] +
+                                                       (r0 + quarter * 32)));
         if (!mbar_wait(&bars[L::bSFull], (uint32_t)i & 1u, abort_flag, status, 0x3A00)) { ok = false; break; }
         if (!mbar_wait(&bars[L::bAuxFull + s], par2, abort_flag, status, 0x3A80)) { ok = false; break; }
         tc_fence_after();
@@ -493,6 +497,7 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
         const int s = i & 1;
         const uint32_t par2 = (uint32_t)(i >> 1) & 1u;
         const int nbase = (cb_lo + i) * kNB + cbase;     // first key of this thread's columns
+        if (p.has_bias && p.bias_vec) asm volatile("prefetch.global.L2 [%0];" ::"l"(bias_row + nbase));
         if (!mbar_wait(&bars[L::bSFull], (uint32_t)i & 1u, abort_flag, status, 0x3C00)) { ok = false; break; }
         tc_fence_after();
         float pr[32];

@@ -370,6 +370,12 @@ sm100_fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ CUten
     for (int j = 0; j < nblk; ++j) {
       const int n0 = (jb_lo + j) * kBN;
       const uint32_t par = (uint32_t)j & 1u;
+      if (p.has_bias && p.bias_vec) {
+        // the thread's 256 bytes of bias for this block: on their way to L2 while the tensor pipe computes S
+        const char* bp = reinterpret_cast<const char*>(bias_row + n0);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(bp));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(bp + 128));
+      }
       if (!mbar_wait(&bars[L::bSFull + t], par, abort_flag, status, 0x700 + 2 * j + t)) { ok = false; break; }
       AB200_FSTAMP(j, 0);
       tc_fence_after();
