@@ -177,6 +177,17 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           tma_load_4d(smem + L::kLate + s * L::kStr + b * L::kStrBox, &tm_late, &bars[L::bLateFull + s], b * 64, srow, hs,
                       sq.bidx);
         issued_l = i + 1;
+        if constexpr (MODE == kWideDQ) {
+          // the next block's K and V towards L2 (their slots free up a block from now; measured: dQ 6 %
+          // faster, while for dV and dK, whose streamed Q and dO are shared by fewer CTAs, it did not pay)
+          if (i + 1 < niter) {
+            const int nrow = (int)(col_tok0 + (int64_t)(cb_lo + cb) * kNB);
+            for (int b = 0; b < L::kBoxes; ++b) {
+              tma_prefetch_4d(&tm_late, b * 64, nrow, hk, sq.bidx);
+              tma_prefetch_4d(&tm_early, b * 64, nrow, hk, sq.bidx);
+            }
+          }
+        }
       }
       if (*abort_flag) {
         // Let copies that are still in flight land before the CTA gives its shared memory back.
