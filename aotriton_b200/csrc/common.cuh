@@ -147,16 +147,21 @@ struct DropoutCtx {
   int32_t threshold;
 };
 
-__device__ __forceinline__ DropoutCtx dropout_ctx(const Params& p, int z, int h) {
+// `seed` and `offset` (= philox_offset1 + philox_offset2) as read from the device scalars: a kernel
+// that walks several heads reads them once and builds each head's context from the values.
+__device__ __forceinline__ DropoutCtx dropout_ctx_from(const Params& p, uint64_t seed, uint64_t offset, int z, int h) {
   DropoutCtx d;
-  d.seed = p.seed_ptr ? *p.seed_ptr : 0ull;
-  uint64_t base = p.off2 + (p.off1_ptr ? *p.off1_ptr : 0ull);
+  d.seed = seed;
   d.stride = (uint32_t)((p.max_sk + 3) / 4);
   int hq_total = p.philox_hq > 0 ? p.philox_hq : p.hq;
   uint64_t zh = (uint64_t)z * hq_total + (uint64_t)(h + p.philox_head_offset);
-  d.base = base + zh * (uint64_t)p.max_sq * d.stride;
+  d.base = offset + zh * (uint64_t)p.max_sq * d.stride;
   d.threshold = p.idropout;
   return d;
+}
+
+__device__ __forceinline__ DropoutCtx dropout_ctx(const Params& p, int z, int h) {
+  return dropout_ctx_from(p, p.seed_ptr ? *p.seed_ptr : 0ull, p.off2 + (p.off1_ptr ? *p.off1_ptr : 0ull), z, h);
 }
 
 // The four 32-bit words of one counter serve columns 4c..4c+3 in the order w0, w2, w1, w3.

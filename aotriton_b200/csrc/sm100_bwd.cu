@@ -603,8 +603,11 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     const int cbase = kWgCols * wg;
     uint32_t G = 0, live = 0, drawn = 0;
     bool ok = true;
-    PhiloxKeys pkeys;      // Philox round keys: they depend on the seed only
-    if (p.dropout_on) pkeys = philox_keys(p.seed_ptr ? *p.seed_ptr : 0ull);
+    // Philox seed and offset are read once; the round keys depend on the seed only
+    const uint64_t ph_seed = (p.dropout_on && p.seed_ptr) ? *p.seed_ptr : 0ull;
+    const uint64_t ph_off = p.off2 + ((p.dropout_on && p.off1_ptr) ? *p.off1_ptr : 0ull);
+    PhiloxKeys pkeys;
+    if (p.dropout_on) pkeys = philox_keys(ph_seed);
     for (int w = blockIdx.x; ok && w < nitems; w = next_item(drawn++, true)) {
       const DkdvItem it = dkdv_item(p, w);
       if (!it.valid) continue;
@@ -772,7 +775,7 @@ sm100_bwd_dkdv_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           // One Philox counter serves four consecutive keys of one query row, and the four lanes of
           // a quad own exactly such keys (same n >> 2): lane q4 of the quad draws the counters of
           // query rows mbase + q4 + 4k (k = 0..7) for all four keys, then the quad exchanges them.
-          const DropoutCtx dctx = dropout_ctx(p, z, h);
+          const DropoutCtx dctx = dropout_ctx_from(p, ph_seed, ph_off, z, h);
           const int q4 = lane & 3;
           uint32_t mine = 0u;            // nibble k: keep bits of keys 4a..4a+3 for query row mbase + q4 + 4k
 #pragma unroll

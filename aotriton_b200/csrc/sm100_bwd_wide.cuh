@@ -355,8 +355,11 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
     // the tightest bounds over the warp's rows: a block needs masking iff it is not inside them
     const int warp_lo = __reduce_max_sync(0xffffffffu, v_lo), warp_hi = __reduce_min_sync(0xffffffffu, v_hi);
     bool ok = true;
-    PhiloxKeys pkeys;      // Philox round keys: they depend on the seed only
-    if (p.dropout_on) pkeys = philox_keys(p.seed_ptr ? *p.seed_ptr : 0ull);
+    // Philox seed and offset are read once; the round keys depend on the seed only
+    const uint64_t ph_seed = (p.dropout_on && p.seed_ptr) ? *p.seed_ptr : 0ull;
+    const uint64_t ph_off = p.off2 + ((p.dropout_on && p.off1_ptr) ? *p.off1_ptr : 0ull);
+    PhiloxKeys pkeys;
+    if (p.dropout_on) pkeys = philox_keys(ph_seed);
     if constexpr (kKeys) {
       const int n = row;
       for (int i = 0, hg = 0, cb = 0; i < niter; ++i) {
@@ -432,7 +435,7 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
           // One Philox counter serves four consecutive keys of one query row, and the four lanes of
           // a quad own exactly such keys: lane q4 of the quad draws the counters of query rows
           // mbase + q4 + 4k (k = 0..7) for all four keys, then the quad exchanges them.
-          const DropoutCtx dctx = dropout_ctx(p, z, h);
+          const DropoutCtx dctx = dropout_ctx_from(p, ph_seed, ph_off, z, h);
           const int q4 = lane & 3;
           uint32_t mine = 0u;
 #pragma unroll
@@ -496,7 +499,7 @@ sm100_bwd_wide_kernel(const __grid_constant__ Params p, const __grid_constant__ 
       const float dlt = (m < sq.sq) ? p.delta[lrow + m] : 0.f;
       const bool simple = !p.has_bias && !__any_sync(0xffffffffu, fabsf(lse2) > 1.0e6f && lse2 != INFINITY);
       DropoutCtx dctx;
-      if (p.dropout_on) dctx = dropout_ctx(p, z, hrow);
+      if (p.dropout_on) dctx = dropout_ctx_from(p, ph_seed, ph_off, z, hrow);
       const int mm = min(m, sq.sq - 1);
       const T* bias_row = p.has_bias ? reinterpret_cast<const T*>(p.bias.ptr) + (int64_t)sq.bidx * p.bias.s[0] +
                                            (int64_t)hrow * p.bias.s[1] + (int64_t)mm * p.bias.s[2]
