@@ -18,8 +18,10 @@ from _util import ATOL, LSE_ATOL, FUDGE, close, randn_inputs, expected_family, r
 
 pytestmark = pytest.mark.gpu
 
-# AB200_SWEEP_FACTOR=N runs N times as many seeds (an occasional long sweep; the default keeps the suite short)
+# AB200_SWEEP_FACTOR=N runs N times as many seeds, AB200_SWEEP_OFFSET=K starts them at K (an occasional
+# long sweep over other cases; the defaults keep the suite short and fixed)
 SWEEP = max(1, int(os.environ.get("AB200_SWEEP_FACTOR", "1")))
+OFFSET = int(os.environ.get("AB200_SWEEP_OFFSET", "0"))
 
 TL, BR = A.TOP_LEFT, A.BOTTOM_RIGHT
 
@@ -49,7 +51,7 @@ def _draw(seed: int):
 
 
 @pytest.mark.parametrize("family", ["auto", "general", "fused"])
-@pytest.mark.parametrize("seed", range(96 * SWEEP))
+@pytest.mark.parametrize("seed", range(OFFSET, OFFSET + 96 * SWEEP))
 def test_random_shape_vs_oracle(seed, family):
     from _gpu_runner import run_fwd_bwd
     dt, B, Hq, Hk, Sq, Sk, D, Dv, (ct, wl, wr), p, use_bias, bshd = _draw(seed)
@@ -97,7 +99,7 @@ def test_random_shape_vs_oracle(seed, family):
 
 
 @pytest.mark.parametrize("family", ["auto", "general"])
-@pytest.mark.parametrize("seed", range(24 * SWEEP))
+@pytest.mark.parametrize("seed", range(OFFSET, OFFSET + 24 * SWEEP))
 def test_random_compact_varlen_vs_oracle(seed, family):
     """Token-packed sequences of random lengths (empty ones included) in THD storage."""
     import numpy as np
@@ -134,7 +136,7 @@ def test_random_compact_varlen_vs_oracle(seed, family):
 
 
 @pytest.mark.parametrize("family", ["auto", "general"])
-@pytest.mark.parametrize("seed", range(16 * SWEEP))
+@pytest.mark.parametrize("seed", range(OFFSET, OFFSET + 16 * SWEEP))
 def test_random_padded_and_strided_varlen_vs_oracle(seed, family):
     """Padded varlen (rank-4 tensors, lengths from cu_seqlens) and strided varlen (THD storage with gaps,
     offsets from seq_strides) with random lengths, head dims and windows; each sequence against the dense
